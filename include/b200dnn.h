@@ -1,0 +1,209 @@
+/*
+ * b200dnn — C ABI of the B200 (sm_100a) dense hot path that sits behind the
+ * DNNKernels op-dispatch API (matmul!, sdpa!, layernorm!, convolution!, scratch!).
+ *
+ * Conventions
+ *   - Every entry point returns an int status: 0 = ok, otherwise a B200_E* /
+ *     B200_DECLINE_* code; nothing throws or aborts across the boundary.
+ *     b200_last_error() returns the message of the last failure on this thread.
+ *   - All array arguments are raw DEVICE pointers owned by the caller unless the
+ *     name says "host".  The library keeps no caller pointer past the stream work
+ *     of the call.  Work is asynchronous on the context's stream, in call order.
+ *   - Arrays are column-major with the reversed torch shape (the reference's
+ *     layout): a "(M,K) ld" matrix has element (i,k) at i + ld*k.
+ *   - fp16 is IEEE binary16; accumulation is fp32 everywhere.
+ *   - "reference" citations are file:line in the reference project
+ *     (DNNKernels/src/...).
+ */
+#ifndef B200DNN_H
+#define B200DNN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------- status codes */
+enum {
+    B200_OK = 0,
+    B200_EINVAL = 1,         /* null pointer / negative extent / bad enum            */
+    B200_ECUDA = 2,          /* a CUDA runtime or driver call failed                 */
+    B200_ENOMEM = 3,         /* pool or workspace exhausted                          */
+    B200_EKERNEL = 4,        /* a kernel reported a bounded wait that ran out        */
+    /* Planner refusals, the vocabulary of Decline(reason) (kernelplans.jl:21-35). */
+    B200_DECLINE_OPERANDS = 16,  /* :operands  dtype/rank the fast path does not take */
+    B200_DECLINE_EXTENT = 17,    /* :extent    an extent the tiling cannot cover      */
+    B200_DECLINE_ALIGN = 18,     /* :wrapped   stride/pointer a TMA map cannot express*/
+    B200_DECLINE_BIAS = 19,      /* :bias      additive attention mask present        */
+    B200_DECLINE_ELTYPE = 20,    /* :eltype                                            */
+    B200_DECLINE_TILING = 21     /* :tiling    no tile shape fits                      */
+};
+
+enum { B200_F16 = 0, B200_F32 = 1 };
+/* actfn(name) (ops.jl:1684-1685): identity / relu_epi / geluexact, plus gelutanh. */
+enum { B200_EPI_NONE = 0, B200_EPI_RELU = 1, B200_EPI_GELU = 2, B200_EPI_GELU_TANH = 3 };
+
+typedef struct b200_ctx b200_ctx;
+
+/* Device facts, the B200 answer to caps(backend)/DeviceCaps (context.jl:55-68). */
+typedef struct {
+    int32_t coopmat;         /* 1: tensor-core path present                           */
+    int32_t tile;            /* MMA K granule in elements (16 for fp16)               */
+    int32_t subgroup;        /* 32                                                     */
+    int32_t coopmatsubgroup; /* 32                                                     */
+    int32_t sharedbudget;    /* bytes of shared memory one CTA may use                */
+    int32_t workgrouplimit;  /* 1024                                                   */
+    int32_t cores;           /* SM count                                               */
+    int32_t warps;           /* resident warps per SM                                  */
+    int32_t cc_major, cc_minor;
+    int64_t total_mem;
+} b200_caps_t;
+
+/* ------------------------------------------------------- context (Ctx, context.jl:240-331) */
+int b200_ctx_create(int device, b200_ctx** out);
+int b200_ctx_destroy(b200_ctx* ctx);
+int b200_caps(b200_ctx* ctx, b200_caps_t* out);
+/* KernelAbstractions.synchronize(backend): block until the context's stream is idle,
+ * then report any device-side error flag raised by a kernel since the last sync. */
+int b200_sync(b200_ctx* ctx);
+const char* b200_last_error(void);
+const char* b200_version(void);   /* KERNELS_VERSION analogue (DNNKernels.jl:26-72) */
+void* b200_stream(b200_ctx* ctx); /* the cudaStream_t the context launches on      */
+/* Number of kernels this library has launched on the context since creation.       */
+int64_t b200_launch_count(b200_ctx* ctx);
+
+/* CUDA-event timer on the context's stream (Diagnostics.optimes, context.jl:162-221). */
+int b200_timer_start(b200_ctx* ctx);
+int b200_timer_stop(b200_ctx* ctx, float* ms_out); /* records, synchronises, reads */
+
+/* ------------------------------------- memory (Mantle pool / toback, driver.jl:81-115) */
+/* 256-byte aligned device block from the context's cudaMalloc pool (size-class free
+ * lists; blocks return to the pool on free, to the driver on ctx destroy). */
+int b200_pool_alloc(b200_ctx* ctx, size_t bytes, void** dptr);
+int b200_pool_free(b200_ctx* ctx, void* dptr);
+int b200_pool_stats(b200_ctx* ctx, size_t* bytes_in_use, size_t* bytes_reserved);
+int b200_upload(b200_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+int b200_download(b200_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes); /* syncs */
+int b200_upload_async(b200_ctx* ctx, void* dst_dev, const void* src_pinned_host, size_t bytes);
+int b200_download_async(b200_ctx* ctx, void* dst_pinned_host, const void* src_dev, size_t bytes);
+int b200_copy(b200_ctx* ctx, void* dst_dev, const void* src_dev, size_t bytes);
+int b200_fill_bytes(b200_ctx* ctx, void* dst_dev, int byte, size_t bytes);
+int b200_host_alloc(size_t bytes, void** hptr); /* pinned host memory */
+int b200_host_free(void* hptr);
+
+/* Per-op bump workspace: Workspace / reset! / scratch! (workspace.jl:19-106).
+ * Offsets are 256-byte aligned; growth allocates max(need*1.5, 1 MiB) and RETIRES the
+ * old block until the next reset, exactly as the reference does, so pointers handed
+ * out earlier in the same op stay valid. */
+int b200_workspace_reset(b200_ctx* ctx);
+int b200_workspace_scratch(b200_ctx* ctx, size_t bytes, void** dptr);
+int b200_workspace_stats(b200_ctx* ctx, size_t* used, size_t* capacity, int* retired);
+
+/* ------------------------------------------------------------------------- GEMM */
+/*
+ * out(M,N) = epi(T(bias[i] + sum_k A(M,K)[i,k] * B(K,N)[k,j])), per batch plane.
+ * Replaces matmul!/matmul_coopmat! (matmul.jl:78-100,235-273), the external
+ * Lava.coopmat_gemm! it calls (matmul.jl:264,269), padcols_kernel! and
+ * mm_epilogue_kernel! (matmul.jl:182-217), and batchedmatmul! (matmul.jl:364-392)
+ * through nbatch/strides.  bias is (M,) fp16 or NULL and starts the fp32 accumulator;
+ * the activation is applied to the value already rounded to out_dtype.
+ * A is (M,K) with M contiguous (the dense weight hoistpermutes leaves), B is (K,N)
+ * with K contiguous (the activations).  No padding of any extent is required; lda,
+ * ldb, ldo and the plane strides are in elements.
+ */
+int b200_gemm_f16(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
+                  const void* B, int64_t ldb, const void* bias, void* out, int64_t ldo,
+                  int out_dtype, int epilogue, int64_t nbatch, int64_t strideA, int64_t strideB,
+                  int64_t strideO);
+/* mm_coopmat_plan (matmul.jl:172-179): B200_OK if the tensor-core kernel takes the
+ * shape, else the Decline reason.  Callable before out is allocated. */
+int b200_gemm_f16_supported(int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldo,
+                            int out_dtype);
+/* The tile plan the GEMM would run with (MMCoopMatPlan, kernelplans.jl:382-385). */
+typedef struct {
+    int32_t block_m, block_n, block_k, stages;
+    int32_t tiles_m, tiles_n, ctas;
+    int32_t smem_bytes;
+} b200_gemm_plan_t;
+int b200_gemm_f16_plan(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t nbatch,
+                       b200_gemm_plan_t* plan);
+
+/* -------------------------------------------------------------------- attention */
+/*
+ * Fused non-causal scaled-dot-product attention, single pass, online softmax.
+ * Replaces sdpa!/sdpaflashcm! + attn_flash_cm! + attn_flash_cm_merge!
+ * (attention.jl:773-776, flash.jl:459-1036,1398-1484), the scalar attn_flash!
+ * (flash.jl:160-271, via out_dtype = B200_F32) and the toLE_tiled_* / densify layout
+ * passes (attention.jl:342-396), which are unnecessary here because q/k/v are read
+ * through their strides.  q,k,v are (E,L,H,B) fp16 with element strides
+ * s = {sE,sL,sH,sB}, sE == 1; out is dense (E,Lq,H,B) in out_dtype.
+ * scale multiplies the fp32 scores; softmax is fp32; P is rounded to fp16 before P*V.
+ */
+typedef struct {
+    const void* ptr;
+    int64_t stride[4]; /* elements: E, L, H, B */
+} b200_strided4;
+int b200_attention_f16(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
+                       const b200_strided4* q, const b200_strided4* k, const b200_strided4* v,
+                       void* out, int out_dtype, float scale);
+/* flashcm_plan (flash.jl:1322-1374): B200_OK or the Decline reason. */
+int b200_attention_f16_supported(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
+                                 const int64_t* qstride, const int64_t* kstride,
+                                 const int64_t* vstride, int has_bias);
+
+/* ------------------------------------------------------------------- layer norm */
+/*
+ * layernorm!/layernorm_kernel! (layernorm.jl:44-135): a is (C, groups) contiguous,
+ * in_dtype/out_dtype fp16 or fp32; gamma/beta are (C,) in in_dtype or NULL; mean and
+ * rstd are fp32 (groups,).  fp32 statistics, variance about the mean.
+ */
+int b200_layernorm(b200_ctx* ctx, int64_t groups, int64_t C, const void* a, int in_dtype, void* out,
+                   int out_dtype, float* mean, float* rstd, const void* gamma, const void* beta,
+                   float eps);
+
+/* ------------------------------------------------------- convolution as a GEMM */
+/*
+ * im2col_kernel! (conv_coopmat.jl:246-289): col (MP,CRSP) fp16 column-major from
+ * x (W,H,Cin,N); rows >= NPQ, columns >= KW*KH*Cin and out-of-image taps are zero.
+ */
+int b200_im2col_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW,
+                    int64_t KH, int64_t sx, int64_t sy, int64_t px, int64_t py, int64_t dx,
+                    int64_t dy, int64_t MP, int64_t CRSP, const void* x, void* col);
+/*
+ * convolution! for one group (conv.jl:100-145) lowered as convolution_coopmat!
+ * (conv_coopmat.jl:341-392) does: [im2col unless 1x1/s1/p0] + GEMM with the bias and
+ * activation fused, written straight into out (OW,OH,Cout,N) — no fp32 plane and no
+ * conv_epilogue_kernel! pass.  x (W,H,Cin,N), w (KW,KH,Cin,Cout) fp16.  Scratch comes
+ * from the context's workspace.
+ */
+int b200_conv2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW,
+                    int64_t KH, int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py,
+                    int64_t dx, int64_t dy, const void* x, const void* w, const void* bias,
+                    void* out, int out_dtype, int epilogue);
+
+/* ------------------------------------------- encoder glue ops (bandwidth-bound) */
+/* add.Tensor, clamp.default, gelu.default on fp16 (ops.jl:186-197,323-335,1698-1702). */
+int b200_add_f16(b200_ctx* ctx, const void* a, const void* b, void* out, int64_t n);
+int b200_clamp_f16(b200_ctx* ctx, const void* a, void* out, int64_t n, float lo, float hi);
+int b200_act_f16(b200_ctx* ctx, const void* a, void* out, int64_t n, int epilogue);
+/* permutedims!/contiguous of a 4-D array (execute.jl:257-277): out dense with shape
+ * shape[0..3] (fastest first), element (i0,i1,i2,i3) read from
+ * src[i0*s[0]+i1*s[1]+i2*s[2]+i3*s[3]]; elsize 2 or 4 bytes. */
+int b200_permute4(b200_ctx* ctx, const void* src, void* out, const int64_t* shape,
+                  const int64_t* stride, int elsize);
+
+/* ---------------------------------------------------------------- sharding layer */
+/*
+ * New surface (no reference counterpart): independent units (images, sequences, GEMM
+ * rows) are split into contiguous ranges, rank r of world gets [begin,end), with split
+ * points rounded to a multiple of align so a GEMM shard starts on a tile boundary.
+ */
+int b200_shard_range(int64_t total, int world, int rank, int64_t align, int64_t* begin,
+                     int64_t* end);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200DNN_H */

@@ -1,0 +1,23 @@
+"""juliavision_b200 — the B200 (sm_100a) dense hot path of DNNKernels behind its own op API.
+
+Host-side mirror of the reference's kernel entry points (`matmul!`, `batchedmatmul!`, `sdpa`,
+`sdpa!`, `layernorm!`, `convolution!`, `scratch!`, `caps`, `toback`) over the C ABI of
+libb200dnn.so.  Importing the package does not need a GPU; creating a `Ctx` does, and there
+is no fallback if the library is missing.
+"""
+from ._lib import B200Error, SO_PATH, lib
+from .attention import sdpa, sdpa_, sdpaplan
+from .context import Ctx, DeviceArray, DeviceCaps, Workspace, caps
+from .conv import convolution_, convsize, onebyone
+from .elementwise import act_, add_, clamp_
+from .kernelplans import AttnScalarPlan, Decline, FlashTCPlan, MMScalarPlan, MMTilePlan
+from .layernorm import layernorm_, native_layer_norm
+from .matmul import batchedmatmul_, matmul_, mmplan
+from .shard import gather_shards, shard_range, shard_range_py
+
+__all__ = [
+    "B200Error", "SO_PATH", "lib", "sdpa", "sdpa_", "sdpaplan", "Ctx", "DeviceArray", "DeviceCaps", "Workspace",
+    "caps", "convolution_", "convsize", "onebyone", "act_", "add_", "clamp_", "AttnScalarPlan", "Decline",
+    "FlashTCPlan", "MMScalarPlan", "MMTilePlan", "layernorm_", "native_layer_norm", "batchedmatmul_", "matmul_",
+    "mmplan", "shard_range", "shard_range_py", "gather_shards",
+]

@@ -1,0 +1,73 @@
+"""sdpa / sdpaplan / sdpa! for the B200 backend (reference kernels/extern/attention.jl:712-834,
+kernels/extern/flash.jl:1322-1484).
+
+q, k, v are (E, L, H, B) views with any strides along L, H, B (E contiguous); out is dense
+(E, Lq, H, B).  Non-causal; `bias` (an additive mask) is declined, as flashcm_plan does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from math import sqrt
+from typing import Optional
+
+import numpy as np
+
+from . import _lib
+from ._lib import B200Error, check
+from .context import Ctx, DeviceArray, dtcode
+from .kernelplans import AttnScalarPlan, Decline, FlashTCPlan
+
+
+def _s4(a: DeviceArray) -> "_lib.Strided4":
+    s = _lib.Strided4()
+    s.ptr = a.ptr
+    for i in range(4):
+        s.stride[i] = a.strides[i]
+    return s
+
+
+def sdpaplan(ctx: Ctx, q: DeviceArray, k: DeviceArray, v: DeviceArray, bias=None):
+    """One decision before `out` exists: FlashTCPlan, AttnScalarPlan or Decline(reason)."""
+    if bias is not None:
+        return Decline("bias")
+    if any(a.dtype != np.float16 for a in (q, k, v)):
+        return Decline("eltype")
+    if any(a.ndim != 4 for a in (q, k, v)):
+        return Decline("operands")
+    E, Lq, H, B = q.shape
+    Lk = k.shape[1]
+    if k.shape != (E, Lk, H, B) or v.shape != (E, Lk, H, B):
+        return Decline("extent")
+    arr = lambda a: (C.c_int64 * 4)(*a.strides)
+    rc = _lib.lib().b200_attention_f16_supported(E, Lq, Lk, H, B, arr(q), arr(k), arr(v), 0)
+    if rc == _lib.OK and all(a.ptr % 16 == 0 for a in (q, k, v)):
+        return FlashTCPlan()
+    if any(a.strides[0] != 1 and a.shape[0] != 1 for a in (q, k, v)):
+        return Decline("wrapped")  # E must be contiguous; densify first (attention.jl:734-759)
+    if rc in (_lib.OK, 18, 21):
+        return AttnScalarPlan(_lib.DECLINE.get(rc, "wrapped"))
+    return Decline(_lib.DECLINE.get(rc, "extent"))
+
+
+def sdpa_(ctx: Ctx, plan, out: Optional[DeviceArray], q, k, v, bias, scale: float) -> DeviceArray:
+    """sdpa!(ctx, plan, out, q, k, v, bias, scale) (attention.jl:773-776)."""
+    if isinstance(plan, Decline):
+        raise B200Error(16, f"sdpa!: Decline(:{plan.reason}); there is no CPU path behind this entry point")
+    E, Lq, H, B = q.shape
+    Lk = k.shape[1]
+    if out is None:
+        # sdpaout: accum(eltype(q)) = fp32 when the caller gives no destination (attention.jl:761-765)
+        out = ctx.allocate(np.float32, E, Lq, H, B)
+    if not out.isdense() or out.shape != (E, Lq, H, B):
+        raise B200Error(17, "sdpa!: out must be dense (E, Lq, H, B)")
+    qs, ks, vs = _s4(q), _s4(k), _s4(v)
+    check(_lib.lib().b200_attention_f16(ctx.handle, E, Lq, Lk, H, B, C.byref(qs), C.byref(ks), C.byref(vs), out.ptr,
+                                        dtcode(out.dtype), float(scale)))
+    return out
+
+
+def sdpa(ctx: Ctx, q, k, v, bias=None, scale: Optional[float] = None, out: Optional[DeviceArray] = None):
+    """sdpa(ctx, q, k, v, bias, scale; out) (attention.jl:712-719)."""
+    if scale is None:
+        scale = 1.0 / sqrt(q.shape[0])
+    return sdpa_(ctx, sdpaplan(ctx, q, k, v, bias), out, q, k, v, bias, scale)

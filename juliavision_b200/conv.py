@@ -1,0 +1,48 @@
+"""convolution! lowered to the tensor-core GEMM (reference kernels/extern/conv.jl:100-145,
+kernels/extern/conv_coopmat.jl:30-392).  x (W,H,Cin,N), w (KW,KH,Cin,Cout), out (OW,OH,Cout,N)."""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import B200Error, check
+from .context import Ctx, DeviceArray, dtcode
+
+
+def convsize(n: int, k: int, s: int, p: int, d: int) -> int:
+    """ATen's output extent (conv.jl:309)."""
+    return (n + 2 * p - d * (k - 1) - 1) // s + 1
+
+
+def onebyone(w: DeviceArray, stride, padding, dilation, groups: int) -> bool:
+    """The 1x1 case that is a plain GEMM (conv.jl:53-88)."""
+    return (w.shape[0] == 1 and w.shape[1] == 1 and tuple(stride) == (1, 1) and tuple(padding) == (0, 0)
+            and tuple(dilation) == (1, 1) and groups == 1)
+
+
+def convolution_(ctx: Ctx, out: DeviceArray, x: DeviceArray, w: DeviceArray, bias: Optional[DeviceArray],
+                 stride: Sequence[int], padding: Sequence[int], dilation: Sequence[int], groups: int = 1,
+                 act: str = "identity") -> DeviceArray:
+    """convolution!(ctx, out, x, w, bias, stride, padding, dilation, groups; act); stride etc. are
+    (x, y) in the reference's reversed order."""
+    if groups != 1:
+        raise B200Error(17, "convolution!: Decline(:groups) — grouped convolutions are not lowered to the GEMM")
+    if x.dtype != np.float16 or w.dtype != np.float16:
+        raise B200Error(16, "convolution!: Decline(:operands)")
+    if not (x.isdense() and w.isdense() and out.isdense()):
+        raise B200Error(18, "convolution!: Decline(:wrapped)")
+    W, H, Cin, N = x.shape
+    KW, KH, Cin2, Cout = w.shape
+    if Cin2 != Cin:
+        raise B200Error(17, "convolution!: channel mismatch")
+    OW = convsize(W, KW, stride[0], padding[0], dilation[0])
+    OH = convsize(H, KH, stride[1], padding[1], dilation[1])
+    if out.shape != (OW, OH, Cout, N):
+        raise B200Error(17, f"convolution!: out is {out.shape}, expected {(OW, OH, Cout, N)}")
+    check(_lib.lib().b200_conv2d_f16(ctx.handle, W, H, Cin, N, KW, KH, Cout, stride[0], stride[1], padding[0],
+                                     padding[1], dilation[0], dilation[1], x.ptr, w.ptr,
+                                     bias.ptr if bias is not None else None, out.ptr, dtcode(out.dtype),
+                                     _lib.EPI[act]))
+    return out

@@ -1,0 +1,185 @@
+// Bandwidth-bound glue ops the encoder graphs run between the dense kernels: residual add,
+// clamp, standalone activation and the strided -> dense copy behind permute/contiguous.
+// fp16 storage, fp32 arithmetic, one rounding at the store (reference ops.jl:186-197,
+// 323-335, 1698-1702; execute.jl:257-277).
+#include <cuda_fp16.h>
+
+#include "internal.h"
+
+namespace b200 {
+
+__device__ __forceinline__ float glue_erf(float x) {
+    float a = fabsf(x);
+    float t = __fdividef(1.0f, 1.0f + 0.3275911f * a);
+    float y = 1.0f - (((((1.061405429f * t - 1.453152027f) * t) + 1.421413741f) * t - 0.284496736f) * t +
+                      0.254829592f) * t * __expf(-a * a);
+    return x < 0.f ? -y : y;
+}
+__device__ __forceinline__ float glue_act(int epi, float v) {
+    switch (epi) {
+        case B200_EPI_RELU: return fmaxf(v, 0.f);
+        case B200_EPI_GELU: return 0.5f * v * (1.0f + glue_erf(v * 0.70710678118654752f));
+        case B200_EPI_GELU_TANH: {
+            float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+            return 0.5f * v * (1.0f + tanhf(u));
+        }
+        default: return v;
+    }
+}
+
+enum { OP_ADD = 0, OP_CLAMP = 1, OP_ACT = 2 };
+
+template <int OP>
+__device__ __forceinline__ float ew(float a, float b, float lo, float hi, int epi) {
+    if (OP == OP_ADD) return a + b;
+    if (OP == OP_CLAMP) return fminf(fmaxf(a, lo), hi);
+    return glue_act(epi, a);
+}
+
+// 8 halfs (16 B) per thread per step, grid-stride; the scalar tail is handled by the last
+// few threads of the same launch.
+template <int OP>
+__global__ void __launch_bounds__(256)
+ew_f16_kernel(const __half* __restrict__ a, const __half* __restrict__ b, __half* __restrict__ out,
+              int64_t n, float lo, float hi, int epi, int vec) {
+    const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+    int64_t done = 0;
+    if (vec) {
+        const int64_t nv = n / 8;
+        for (int64_t i = tid; i < nv; i += nthreads) {
+            uint4 ua = __ldg(reinterpret_cast<const uint4*>(a) + i);
+            uint4 ub = OP == OP_ADD ? __ldg(reinterpret_cast<const uint4*>(b) + i) : ua;
+            uint4 uo;
+            const __half2* ha = reinterpret_cast<const __half2*>(&ua);
+            const __half2* hb = reinterpret_cast<const __half2*>(&ub);
+            __half2* ho = reinterpret_cast<__half2*>(&uo);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float2 fa = __half22float2(ha[q]), fb = __half22float2(hb[q]);
+                ho[q] = __floats2half2_rn(ew<OP>(fa.x, fb.x, lo, hi, epi), ew<OP>(fa.y, fb.y, lo, hi, epi));
+            }
+            reinterpret_cast<uint4*>(out)[i] = uo;
+        }
+        done = nv * 8;
+    }
+    for (int64_t i = done + tid; i < n; i += nthreads) {
+        float fa = __half2float(a[i]);
+        float fb = OP == OP_ADD ? __half2float(b[i]) : 0.f;
+        out[i] = __float2half_rn(ew<OP>(fa, fb, lo, hi, epi));
+    }
+}
+
+template <int OP>
+static int launch_ew(b200_ctx* ctx, const void* a, const void* b, void* out, int64_t n, float lo, float hi,
+                     int epi) {
+    if (n == 0) return B200_OK;
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const int vec = al(a) && al(out) && (OP != OP_ADD || al(b));
+    int64_t work = vec ? cdiv(n, 8) : n;
+    int64_t blocks = cdiv(work, 256);
+    const int64_t cap = (int64_t)ctx->prop.multiProcessorCount * 16;
+    if (blocks > cap) blocks = cap;
+    ew_f16_kernel<OP><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const __half*)a, (const __half*)b, (__half*)out,
+                                                                  n, lo, hi, epi, vec);
+    ctx->launches++;
+    B200_CUDA(cudaGetLastError());
+    return B200_OK;
+}
+
+// Strided gather into a dense array: one thread per output element, output-coalesced.
+template <typename T>
+__global__ void __launch_bounds__(256)
+permute4_kernel(const T* __restrict__ src, T* __restrict__ out, int64_t n, int64_t d0, int64_t d1, int64_t d2,
+                int64_t s0, int64_t s1, int64_t s2, int64_t s3) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t i0 = i % d0, t = i / d0;
+        int64_t i1 = t % d1;
+        t /= d1;
+        int64_t i2 = t % d2, i3 = t / d2;
+        out[i] = src[i0 * s0 + i1 * s1 + i2 * s2 + i3 * s3];
+    }
+}
+
+// Same gather when the source is contiguous along output axis 1 (a transpose of the two
+// fastest axes, the layout change behind permute(0,2,1,3)-style views): 32x32 tiles through
+// shared memory so both the reads and the writes coalesce.
+template <typename T>
+__global__ void __launch_bounds__(256)
+transpose01_kernel(const T* __restrict__ src, T* __restrict__ out, int d0, int d1, int64_t d2, int64_t s0,
+                   int64_t s2, int64_t s3) {
+    __shared__ T tile[32][33];
+    const int64_t z = blockIdx.z;
+    const int64_t i2 = z % d2, i3 = z / d2;
+    const T* sp = src + i2 * s2 + i3 * s3;
+    T* op = out + z * (int64_t)d0 * d1;
+    const int b0 = blockIdx.x * 32, b1 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int r = ty; r < 32; r += 8) {
+        int i0 = b0 + r, i1 = b1 + tx; // read: i1 fastest in the source
+        if (i0 < d0 && i1 < d1) tile[r][tx] = sp[(int64_t)i0 * s0 + i1];
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+        int i1 = b1 + r, i0 = b0 + tx; // write: i0 fastest in the output
+        if (i0 < d0 && i1 < d1) op[i0 + (int64_t)d0 * i1] = tile[tx][r];
+    }
+}
+
+template <typename T>
+static int launch_permute(b200_ctx* ctx, const void* src, void* out, const int64_t* d, const int64_t* s) {
+    const int64_t n = d[0] * d[1] * d[2] * d[3];
+    if (n == 0) return B200_OK;
+    if (s[1] == 1 && s[0] != 1 && d[0] < (1ll << 30) && d[1] < (1ll << 30) && d[2] * d[3] < 65536 &&
+        cdiv(d[1], 32) < 65536) {
+        dim3 grid((unsigned)cdiv(d[0], 32), (unsigned)cdiv(d[1], 32), (unsigned)(d[2] * d[3]));
+        transpose01_kernel<T><<<grid, 256, 0, ctx->stream>>>((const T*)src, (T*)out, (int)d[0], (int)d[1], d[2], s[0],
+                                                            s[2], s[3]);
+    } else {
+        int64_t blocks = cdiv(n, 256);
+        const int64_t cap = (int64_t)ctx->prop.multiProcessorCount * 32;
+        if (blocks > cap) blocks = cap;
+        permute4_kernel<T><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const T*)src, (T*)out, n, d[0], d[1], d[2], s[0],
+                                                                     s[1], s[2], s[3]);
+    }
+    ctx->launches++;
+    B200_CUDA(cudaGetLastError());
+    return B200_OK;
+}
+
+} // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_add_f16(b200_ctx* ctx, const void* a, const void* b, void* out, int64_t n) {
+    B200_REQUIRE(ctx && n >= 0 && (n == 0 || (a && b && out)), B200_EINVAL, "add: bad argument");
+    B200_CUDA(cudaSetDevice(ctx->device));
+    return launch_ew<OP_ADD>(ctx, a, b, out, n, 0.f, 0.f, 0);
+}
+int b200_clamp_f16(b200_ctx* ctx, const void* a, void* out, int64_t n, float lo, float hi) {
+    B200_REQUIRE(ctx && n >= 0 && (n == 0 || (a && out)), B200_EINVAL, "clamp: bad argument");
+    B200_CUDA(cudaSetDevice(ctx->device));
+    return launch_ew<OP_CLAMP>(ctx, a, nullptr, out, n, lo, hi, 0);
+}
+int b200_act_f16(b200_ctx* ctx, const void* a, void* out, int64_t n, int epilogue) {
+    B200_REQUIRE(ctx && n >= 0 && (n == 0 || (a && out)), B200_EINVAL, "act: bad argument");
+    B200_REQUIRE(epilogue >= B200_EPI_NONE && epilogue <= B200_EPI_GELU_TANH, B200_EINVAL, "act: epilogue %d",
+                 epilogue);
+    B200_CUDA(cudaSetDevice(ctx->device));
+    return launch_ew<OP_ACT>(ctx, a, nullptr, out, n, 0.f, 0.f, epilogue);
+}
+int b200_permute4(b200_ctx* ctx, const void* src, void* out, const int64_t* shape, const int64_t* stride,
+                  int elsize) {
+    B200_REQUIRE(ctx && shape && stride, B200_EINVAL, "permute4: null argument");
+    for (int i = 0; i < 4; ++i) B200_REQUIRE(shape[i] >= 0, B200_EINVAL, "permute4: negative extent");
+    B200_REQUIRE(elsize == 2 || elsize == 4, B200_DECLINE_ELTYPE, "permute4: element size %d", elsize);
+    if (shape[0] * shape[1] * shape[2] * shape[3] == 0) return B200_OK;
+    B200_REQUIRE(src && out, B200_EINVAL, "permute4: null array");
+    B200_CUDA(cudaSetDevice(ctx->device));
+    return elsize == 2 ? launch_permute<uint16_t>(ctx, src, out, shape, stride)
+                       : launch_permute<uint32_t>(ctx, src, out, shape, stride);
+}
+
+} // extern "C"

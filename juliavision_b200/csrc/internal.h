@@ -1,0 +1,84 @@
+// Library-internal declarations shared by the translation units of libb200dnn.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/b200dnn.h"
+
+namespace b200 {
+
+int fail(int code, const char* fmt, ...);  // records the thread's last error, returns code
+int fail_cuda(cudaError_t e, const char* what);
+
+#define B200_CUDA(call)                                         \
+    do {                                                        \
+        cudaError_t _e = (call);                                \
+        if (_e != cudaSuccess) return ::b200::fail_cuda(_e, #call); \
+    } while (0)
+
+#define B200_REQUIRE(cond, code, ...)                        \
+    do {                                                     \
+        if (!(cond)) return ::b200::fail((code), __VA_ARGS__); \
+    } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct RetiredBlock {
+    void* ptr;
+    size_t bytes;
+};
+
+} // namespace b200
+
+struct b200_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaDeviceProp prop{};
+    int* d_status = nullptr;   // device status words: [0] first failed wait code
+    int64_t launches = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    b200::EncodeTiledFn encode = nullptr;
+
+    // cudaMalloc pool: free blocks by size, live blocks by pointer.
+    std::mutex mu;
+    std::multimap<size_t, void*> free_blocks;
+    std::unordered_map<void*, size_t> live_blocks;
+    size_t bytes_in_use = 0, bytes_reserved = 0;
+
+    // Per-op bump workspace.
+    void* ws_buf = nullptr;
+    size_t ws_cap = 0, ws_used = 0;
+    std::vector<b200::RetiredBlock> ws_retired;
+};
+
+namespace b200 {
+
+// Encode a tiled tensor map of `rank` dims (innermost first).  strides_bytes has rank-1
+// entries (the innermost stride is the element size).
+int make_tmap(b200_ctx* ctx, CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base,
+              const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+              CUtensorMapSwizzle swz);
+
+int pool_alloc(b200_ctx* ctx, size_t bytes, void** out);
+int pool_free(b200_ctx* ctx, void* p);
+int ws_scratch(b200_ctx* ctx, size_t bytes, void** out);
+
+// GEMM with the bias broadcast along either axis (bias_per_n = 1: one value per column j,
+// which is what a convolution lowered to a GEMM over pixels needs).
+int gemm_f16_run(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
+                 int64_t ldb, const void* bias, int bias_per_n, void* out, int64_t ldo, int out_dtype,
+                 int epilogue, int64_t nbatch, int64_t strideA, int64_t strideB, int64_t strideO);
+
+inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+} // namespace b200

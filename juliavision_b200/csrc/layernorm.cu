@@ -1,0 +1,248 @@
+// LayerNorm over the leading (contiguous) axis: one read of the input, one write of the
+// output.  Bandwidth-bound: 16-byte vector loads, the whole group held in registers, fp32
+// statistics reduced with warp shuffles, variance taken about the mean (two passes over
+// registers, never E[x^2]-mean^2).
+//
+// Replaces layernorm_kernel! (reference kernels/layernorm.jl:44-114): 128 threads per
+// group, shared-memory tree reductions and three strided passes over the group.
+#include <cuda_fp16.h>
+
+#include "internal.h"
+
+namespace b200 {
+
+template <typename T> struct Vec16;
+template <> struct Vec16<__half> {
+    static constexpr int N = 8;
+    uint4 raw;
+    __device__ __forceinline__ void to_f32(float* f) const {
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 t = __half22float2(h[i]);
+            f[2 * i] = t.x;
+            f[2 * i + 1] = t.y;
+        }
+    }
+};
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    uint4 raw;
+    __device__ __forceinline__ void to_f32(float* f) const {
+        const float* p = reinterpret_cast<const float*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = p[i];
+    }
+};
+
+template <int N> __device__ __forceinline__ void store_vec(__half* dst, const float* f) {
+    static_assert(N == 8 || N == 4, "vector width");
+    if constexpr (N == 8) {
+        uint4 o;
+        __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        *reinterpret_cast<uint4*>(dst) = o;
+    } else {
+        uint2 o;
+        __half2* h = reinterpret_cast<__half2*>(&o);
+        h[0] = __floats2half2_rn(f[0], f[1]);
+        h[1] = __floats2half2_rn(f[2], f[3]);
+        *reinterpret_cast<uint2*>(dst) = o;
+    }
+}
+template <int N> __device__ __forceinline__ void store_vec(float* dst, const float* f) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4)
+        *reinterpret_cast<float4*>(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// One warp per group; lane l owns vectors l, l+32, ... (VPL of them at most).
+template <typename InT, typename OutT, int VPL>
+__global__ void __launch_bounds__(128)
+ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restrict__ mean,
+               float* __restrict__ rstd, const InT* __restrict__ gamma,
+               const InT* __restrict__ beta, int64_t groups, int C, float eps) {
+    constexpr int VN = Vec16<InT>::N;
+    const int lane = threadIdx.x & 31;
+    const int64_t g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (g >= groups) return;
+    const int nvec = C / VN;
+    const InT* src = a + g * (int64_t)C;
+
+    float x[VPL][VN];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        int v = lane + 32 * i;
+        if (v < nvec) {
+            Vec16<InT> t;
+            t.raw = __ldg(reinterpret_cast<const uint4*>(src) + v);
+            t.to_f32(x[i]);
+#pragma unroll
+            for (int j = 0; j < VN; ++j) s += x[i][j];
+        }
+    }
+    const float n = (float)C;
+    const float mu = warp_sum(s) / n;
+    float s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        if (lane + 32 * i < nvec) {
+#pragma unroll
+            for (int j = 0; j < VN; ++j) {
+                float d = x[i][j] - mu;
+                s2 += d * d;
+            }
+        }
+    }
+    const float r = 1.0f / sqrtf(warp_sum(s2) / n + eps);
+
+    OutT* dst = out + g * (int64_t)C;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        int v = lane + 32 * i;
+        if (v < nvec) {
+            float y[VN];
+#pragma unroll
+            for (int j = 0; j < VN; ++j) y[j] = (x[i][j] - mu) * r;
+            if (gamma) {
+                Vec16<InT> t;
+                float gf[VN];
+                t.raw = __ldg(reinterpret_cast<const uint4*>(gamma) + v);
+                t.to_f32(gf);
+#pragma unroll
+                for (int j = 0; j < VN; ++j) y[j] *= gf[j];
+            }
+            if (beta) {
+                Vec16<InT> t;
+                float bf[VN];
+                t.raw = __ldg(reinterpret_cast<const uint4*>(beta) + v);
+                t.to_f32(bf);
+#pragma unroll
+                for (int j = 0; j < VN; ++j) y[j] += bf[j];
+            }
+            store_vec<VN>(dst + (int64_t)v * VN, y);
+        }
+    }
+    if (lane == 0) {
+        mean[g] = mu;
+        rstd[g] = r;
+    }
+}
+
+__device__ __forceinline__ float ldf(const __half* p, int64_t i) { return __half2float(p[i]); }
+__device__ __forceinline__ float ldf(const float* p, int64_t i) { return p[i]; }
+__device__ __forceinline__ void stf(__half* p, int64_t i, float v) { p[i] = __float2half_rn(v); }
+__device__ __forceinline__ void stf(float* p, int64_t i, float v) { p[i] = v; }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    float t = l < nw ? red[l] : 0.f;
+    return warp_sum(t);
+}
+
+// Any C, any alignment: one block per group, scalar accesses, the group re-read from
+// L1/L2 for the second and third pass.
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(256)
+ln_block_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restrict__ mean,
+                float* __restrict__ rstd, const InT* __restrict__ gamma,
+                const InT* __restrict__ beta, int64_t C, float eps) {
+    __shared__ float red[32];
+    const int64_t g = blockIdx.x;
+    const InT* src = a + g * C;
+    float s = 0.f;
+    for (int64_t i = threadIdx.x; i < C; i += blockDim.x) s += ldf(src, i);
+    const float n = (float)C;
+    const float mu = block_sum(s, red) / n;
+    float s2 = 0.f;
+    for (int64_t i = threadIdx.x; i < C; i += blockDim.x) {
+        float d = ldf(src, i) - mu;
+        s2 += d * d;
+    }
+    const float r = 1.0f / sqrtf(block_sum(s2, red) / n + eps);
+    OutT* dst = out + g * C;
+    for (int64_t i = threadIdx.x; i < C; i += blockDim.x) {
+        float y = (ldf(src, i) - mu) * r;
+        if (gamma) y *= ldf(gamma, i);
+        if (beta) y += ldf(beta, i);
+        stf(dst, i, y);
+    }
+    if (threadIdx.x == 0) {
+        mean[g] = mu;
+        rstd[g] = r;
+    }
+}
+
+template <typename InT, typename OutT>
+static int launch_ln(b200_ctx* ctx, int64_t groups, int64_t C, const void* a, void* out, float* mean,
+                     float* rstd, const void* gamma, const void* beta, float eps) {
+    constexpr int VN = Vec16<InT>::N;
+    const InT* ap = static_cast<const InT*>(a);
+    OutT* op = static_cast<OutT*>(out);
+    const InT* gp = static_cast<const InT*>(gamma);
+    const InT* bp = static_cast<const InT*>(beta);
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const size_t out_vec_bytes = VN * sizeof(OutT);
+    bool vec_ok = C % VN == 0 && C / VN <= 32 * 16 && al16(a) && (!gamma || al16(gamma)) &&
+                  (!beta || al16(beta)) &&
+                  (reinterpret_cast<uintptr_t>(out) % (out_vec_bytes > 16 ? 16 : out_vec_bytes)) == 0;
+    if (vec_ok) {
+        const int nvec = (int)(C / VN);
+        const int vpl = (nvec + 31) / 32;
+        const int wpb = 4;
+        dim3 grid((unsigned)cdiv(groups, wpb)), block(32 * wpb);
+#define LN_GO(V)                                                                                   \
+    ln_warp_kernel<InT, OutT, V><<<grid, block, 0, ctx->stream>>>(ap, op, mean, rstd, gp, bp, groups, \
+                                                                  (int)C, eps)
+        if (vpl <= 1) LN_GO(1);
+        else if (vpl <= 2) LN_GO(2);
+        else if (vpl <= 4) LN_GO(4);
+        else if (vpl <= 8) LN_GO(8);
+        else LN_GO(16);
+#undef LN_GO
+    } else {
+        ln_block_kernel<InT, OutT><<<(unsigned)groups, 256, 0, ctx->stream>>>(ap, op, mean, rstd, gp, bp,
+                                                                             C, eps);
+    }
+    ctx->launches++;
+    B200_CUDA(cudaGetLastError());
+    return B200_OK;
+}
+
+} // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_layernorm(b200_ctx* ctx, int64_t groups, int64_t C, const void* a, int in_dtype,
+                              void* out, int out_dtype, float* mean, float* rstd, const void* gamma,
+                              const void* beta, float eps) {
+    B200_REQUIRE(ctx, B200_EINVAL, "layernorm: null ctx");
+    B200_REQUIRE(groups >= 0 && C > 0, B200_EINVAL, "layernorm: groups=%lld C=%lld", (long long)groups,
+                 (long long)C);
+    if (groups == 0) return B200_OK;
+    B200_REQUIRE(a && out && mean && rstd, B200_EINVAL, "layernorm: null array");
+    B200_REQUIRE(groups < (1ll << 31), B200_DECLINE_EXTENT, "layernorm: %lld groups", (long long)groups);
+    B200_REQUIRE((in_dtype == B200_F16 || in_dtype == B200_F32) &&
+                     (out_dtype == B200_F16 || out_dtype == B200_F32),
+                 B200_DECLINE_ELTYPE, "layernorm: dtype %d -> %d", in_dtype, out_dtype);
+    B200_CUDA(cudaSetDevice(ctx->device));
+    if (in_dtype == B200_F16 && out_dtype == B200_F16)
+        return launch_ln<__half, __half>(ctx, groups, C, a, out, mean, rstd, gamma, beta, eps);
+    if (in_dtype == B200_F16 && out_dtype == B200_F32)
+        return launch_ln<__half, float>(ctx, groups, C, a, out, mean, rstd, gamma, beta, eps);
+    if (in_dtype == B200_F32 && out_dtype == B200_F16)
+        return launch_ln<float, __half>(ctx, groups, C, a, out, mean, rstd, gamma, beta, eps);
+    return launch_ln<float, float>(ctx, groups, C, a, out, mean, rstd, gamma, beta, eps);
+}

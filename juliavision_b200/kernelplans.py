@@ -1,0 +1,51 @@
+"""Plan objects: one decision per call, made before the output is allocated, so that holding
+a plan means the kernel runs (the rule of the reference's kernelplans.jl:1-35 and
+flash.jl:1428-1432).  A refusal is a `Decline(reason)` with the reference's vocabulary.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class Decline:
+    """Structured refusal (kernelplans.jl:21-35). reason is one of :operands, :extent, :wrapped,
+    :bias, :eltype, :tiling, :notvector."""
+    reason: str
+
+
+@dataclass(frozen=True)
+class MMTilePlan:
+    """Tensor-core GEMM plan; stands where MMCoopMatPlan(NP, tile) stood (kernelplans.jl:382-385).
+    No padded extent: ragged M/N/K are covered by TMA-clipped tiles."""
+    block_m: int
+    block_n: int
+    block_k: int
+    stages: int
+    tiles_m: int
+    tiles_n: int
+    ctas: int
+    smem_bytes: int
+
+
+@dataclass(frozen=True)
+class MMScalarPlan:
+    """fp16 operands a tensor map cannot express (unaligned leading dimension or pointer): the
+    one-thread-per-output kernel with mm2's arithmetic (matmul.jl:17-28), still on the GPU."""
+    reason: str
+
+
+@dataclass(frozen=True)
+class FlashTCPlan:
+    """Fused single-pass attention on tcgen05; stands where FlashCMPlan stood
+    (kernelplans.jl:54-324). BR/BC are the query/key block, EP the padded head dim."""
+    BR: int = 128
+    BC: int = 128
+    EP: int = 64
+    nsplit: int = 1
+
+
+@dataclass(frozen=True)
+class AttnScalarPlan:
+    """Fused attention for head dims / strides the tensor-core kernel declines."""
+    reason: str
