@@ -1,0 +1,380 @@
+"""Benchmark of the dense hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the 32-layer encoder stack (BASELINE config 3: d_model 1280, 20 heads,
+FFN 5120 with GELU, pre-LayerNorm, 1500x1280 input, batch 1, fp16, random-init weights) over one
+synthetic input per GPU — layer norm, the projection/FFN GEMMs with fused bias/GELU, fused
+attention and the glue ops, all through the library's public entry points.  With N GPUs each rank
+runs its own input (batch sharding, weights replicated, no data-path collective): weak scaling.
+
+The JSON line reports ms per input ("ms/img") as `value`, the same thing measured end to end with
+the host<->device copies inside the timed region as `e2e`, the tensor-core roofline of the
+dominant kernel (the fp16 GEMM) as `roofline`, per-kernel figures for the other configs under
+`kernels`, and the CPU oracle timed on this box's host cores as `cpu_baseline`.
+
+`--impl reference` times the reference's CPU form of the same path (the C oracle: the Julia
+original cannot run here) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "encoder_ms_per_img"
+UNIT = "ms/img"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(source="measured", hbm_gbs=d["hbm_gbs"], tflops=d["bf16_tflops"],
+                    tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]))
+    return dict(source="fallback", hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([t.strip() for t in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            except (ValueError, IndexError):
+                pass
+        # Under load = the upper half of the samples (the sampler also sees idle gaps).
+        sm.sort()
+        load = sm[len(sm) // 2:] if sm else []
+        return dict(sm_mhz=(load[len(load) // 2] if load else None), sm_max_mhz=mx, samples=len(sm),
+                    reasons=sorted(reasons))
+
+
+def time_region(ctx, fn, reps: int) -> float:
+    """ms per call of fn, CUDA events on the context's own stream, one sync for the batch."""
+    ctx.timer_start()
+    for _ in range(reps):
+        fn()
+    return ctx.timer_stop() / reps
+
+
+def kernel_figures(ctx, jv, pk, quick: bool):
+    """Per-kernel throughput on the other BASELINE configs, each timed alone with CUDA events on
+    inputs that rotate through more than L2's worth of buffers."""
+    import ctypes as C
+    out = {}
+    rng = np.random.default_rng(7)
+
+    def gemm_case(tokens, feats, K, epi="identity", bias=True, nbuf=None):
+        per = (tokens * K + K * feats + tokens * feats) * 2
+        nbuf = nbuf or max(2, min(8, int(300e6 // per) + 1))
+        sets = []
+        for _ in range(nbuf):
+            X = ctx.toback(np.float16(rng.standard_normal((tokens, K), dtype=np.float32) * 0.05))
+            Wt = ctx.toback(np.float16(rng.standard_normal((K, feats), dtype=np.float32) * 0.05))
+            b = ctx.toback(np.float16(rng.standard_normal(feats, dtype=np.float32) * 0.05)) if bias else None
+            sets.append((X, Wt, b, ctx.allocate(np.float16, feats, tokens)))
+        i = [0]
+
+        def go():
+            X, Wt, b, o = sets[i[0] % nbuf]
+            i[0] += 1
+            jv.matmul_(ctx, o, Wt, X, b, epi=epi)
+
+        for _ in range(3):
+            go()
+        ctx.synchronize()
+        reps = 20 if quick else 50
+        ms = time_region(ctx, go, reps)
+        tf = 2.0 * tokens * feats * K / ms / 1e9
+        return dict(ms=round(ms, 5), tflops=round(tf, 1), frac_of_measured_peak=round(tf / pk["tflops"], 4),
+                    frac_of_spec_2250=round(tf / 2250.0, 4), buffers=nbuf)
+
+    out["gemm_config1_4096x3072x768"] = gemm_case(4096, 3072, 768)
+    out["gemm_4096x4096x4096"] = gemm_case(4096, 4096, 4096, bias=False)
+    out["gemm_8192x8192x8192"] = gemm_case(8192, 8192, 8192, bias=False, nbuf=2)
+    out["gemm_ffn1_1500x5120x1280_gelu"] = gemm_case(1500, 5120, 1280, epi="gelu")
+
+    # config 2: attention B1 H12 L4096 E64
+    B, H, L, E = 1, 12, 4096, 64
+    sets = []
+    for _ in range(4):
+        q, k, v = (ctx.toback(np.float16(rng.standard_normal((B, H, L, E), dtype=np.float32))) for _ in range(3))
+        sets.append((q, k, v, ctx.allocate(np.float16, E, L, H, B)))
+    i = [0]
+
+    def att():
+        q, k, v, o = sets[i[0] % 4]
+        i[0] += 1
+        jv.sdpa(ctx, q, k, v, None, 0.125, out=o)
+
+    for _ in range(3):
+        att()
+    ctx.synchronize()
+    ms = time_region(ctx, att, 20 if quick else 50)
+    tf = 4.0 * L * L * E * H * B / ms / 1e9
+    out["attention_config2_L4096_E64_H12"] = dict(ms=round(ms, 5), tflops=round(tf, 1),
+                                                  frac_of_measured_peak=round(tf / pk["tflops"], 4),
+                                                  frac_of_spec_2250=round(tf / 2250.0, 4))
+
+    # layer norm: bandwidth on a tensor larger than L2 (65536 groups x 1280, fp16 in/out)
+    groups, Cn = 65536, 1280
+    a = ctx.toback(np.float16(rng.standard_normal((groups, Cn), dtype=np.float32)))
+    o = ctx.allocate(np.float16, Cn, groups)
+    mean, rstd = ctx.allocate(np.float32, groups), ctx.allocate(np.float32, groups)
+    g = ctx.toback(np.ones(Cn, np.float16))
+    ln = lambda: jv.layernorm_(ctx, o, mean, rstd, a, g, g, Cn, 1e-5)
+    for _ in range(3):
+        ln()
+    ctx.synchronize()
+    ms = time_region(ctx, ln, 20)
+    byts = groups * Cn * 4 + 2 * Cn * 2 + groups * 8
+    out["layernorm_65536x1280"] = dict(ms=round(ms, 5), gbs=round(byts / ms / 1e6, 1),
+                                       frac_of_measured_hbm=round(byts / ms / 1e6 / pk["hbm_gbs"], 4),
+                                       frac_of_spec_8000=round(byts / ms / 1e6 / 8000.0, 4))
+    return out
+
+
+def cpu_baseline(cfg, weights, x, layers: int):
+    """The oracle's encoder on the host cores: `layers` of the stack, extrapolated linearly."""
+    from oracle import oracle as ora
+    from oracle.encoder_ref import oracle_forward
+    t0 = time.perf_counter()
+    oracle_forward(cfg, weights, x, layers=layers)
+    dt = time.perf_counter() - t0
+    ms_full = dt * 1e3 * cfg.layers / layers
+    return dict(value=round(ms_full, 1), unit=UNIT, cores=ora.num_threads(), kind="port",
+                sample=f"{layers} of {cfg.layers} layers of the same encoder on the same input ({dt:.1f} s), "
+                       f"extrapolated linearly to {cfg.layers} layers")
+
+
+def run_reference(args):
+    """The reference's CPU form of the path (C oracle; the Julia original cannot run here)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from juliavision_b200.encoder import EncoderConfig, init_weights
+    cfg = EncoderConfig()
+    layers = 1
+    weights = init_weights(EncoderConfig(layers=layers)) + []
+    x = np.float16(np.random.default_rng(11).standard_normal((cfg.tokens, cfg.d_model), dtype=np.float32))
+    from oracle import oracle as ora
+    from oracle.encoder_ref import oracle_forward
+    wl = weights[:layers] + [weights[-1]]
+    for _ in range(min(args.warmup, 1)):
+        oracle_forward(cfg, wl, x, layers=layers)
+    times = []
+    for _ in range(max(1, min(args.steps, 3))):
+        t0 = time.perf_counter()
+        oracle_forward(cfg, wl, x, layers=layers)
+        times.append(time.perf_counter() - t0)
+    ms = float(np.mean(times)) * 1e3 * cfg.layers / layers
+    line = dict(impl="reference", metric=METRIC, value=round(ms, 1), unit=UNIT, n_gpus=args.gpus, steps=len(times),
+                warmup=min(args.warmup, 1), ms_per_step=round(ms, 1), higher_is_better=False, scaling="weak",
+                vs_baseline=None, dtype="f16 (fp32 accumulate)", data="synthetic",
+                config=dict(workload="config 3: 32-layer pre-LN encoder, d_model 1280, 20 heads, FFN 5120 GELU, "
+                                     "1500x1280 input, batch 1"),
+                cpu_baseline=dict(value=round(ms, 1), unit=UNIT, cores=ora.num_threads(), kind="port",
+                                  sample=f"each step = {layers} of {cfg.layers} layers, extrapolated linearly"),
+                e2e=dict(value=round(ms, 1), unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=32, help="encoder depth (32 = the named config)")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel figures")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--cpu-layers", type=int, default=2)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    import torch
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    import juliavision_b200 as jv
+    from juliavision_b200 import _lib
+    from juliavision_b200.encoder import Encoder, EncoderConfig, init_weights
+    import ctypes as C
+
+    pk = peaks()
+    warmup = max(args.warmup, 3)
+    cfg = EncoderConfig(layers=args.layers)
+    weights = init_weights(cfg)
+    ctx = jv.Ctx(local)
+    enc = Encoder(ctx, cfg, weights)
+    # every rank has its own input (an independent sequence), seeded by rank
+    x = np.float16(np.random.default_rng(11 + rank).standard_normal((cfg.tokens, cfg.d_model), dtype=np.float32))
+    nbytes = x.nbytes
+    hx, hy = C.c_void_p(), C.c_void_p()
+    _lib.check(_lib.lib().b200_host_alloc(nbytes, C.byref(hx)))
+    _lib.check(_lib.lib().b200_host_alloc(nbytes, C.byref(hy)))
+    C.memmove(hx.value, x.ctypes.data, nbytes)
+    ctx.upload(enc.xin, x)
+
+    launches_per_pass = enc.launches_per_pass()
+    ctx.synchronize()
+    graph = enc.capture()
+    for _ in range(warmup):
+        graph.replay()
+    ctx.synchronize()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        ctx.synchronize()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+
+    # ---- device-resident timing: K replays, events on the library's stream
+    barrier()
+    ctx.timer_start()
+    for _ in range(args.steps):
+        graph.replay()
+    ms_total = ctx.timer_stop()
+    barrier()
+    ms_step = ms_total / args.steps
+
+    # ---- dominant kernel alone: every GEMM launch of one pass, in pass order, nothing else between
+    def gemm_pass():
+        d, f, L = cfg.d_model, cfg.ffn, cfg.tokens
+        h = enc._buf("h", np.float16, d, L)
+        q, k, v = (enc._buf(n, np.float16, d, L) for n in ("q", "k", "v"))
+        att_t = enc._buf("att_t", np.float16, d, L)
+        ff = enc._buf("f", np.float16, f, L)
+        for w in enc.layers:
+            jv.matmul_(ctx, q, w["wq"], h, w["bq"])
+            jv.matmul_(ctx, k, w["wk"], h, None)
+            jv.matmul_(ctx, v, w["wv"], h, w["bv"])
+            jv.matmul_(ctx, h, w["wo"], att_t, w["bo"])
+            jv.matmul_(ctx, ff, w["w1"], h, w["b1"], epi="gelu")
+            jv.matmul_(ctx, h, w["w2"], ff, w["b2"])
+
+    gemm_pass()
+    ctx.synchronize()
+    ggraph = ctx.capture(gemm_pass)
+    for _ in range(3):
+        ggraph.replay()
+    ctx.synchronize()
+    gemm_ms = time_region(ctx, ggraph.replay, max(3, args.steps // 2))
+    n_gemm = 6 * cfg.layers
+    gemm_tflops = cfg.gemm_flops() / gemm_ms / 1e9
+
+    # ---- end to end through the public API: H2D of the input and D2H of the result inside the region
+    def e2e_step():
+        _lib.check(_lib.lib().b200_upload_async(ctx.handle, enc.xin.ptr, hx, nbytes))
+        graph.replay()
+        _lib.check(_lib.lib().b200_download_async(ctx.handle, hy, enc.y.ptr, nbytes))
+        ctx.synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    ctx.timer_start()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e_ms = ctx.timer_stop() / args.steps
+    barrier()
+    clocks = sampler.stop()
+
+    # ---- max over ranks
+    if dist is not None:
+        t = torch.tensor([ms_step, e2e_ms], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, e2e_ms = float(t[0]), float(t[1])
+
+    kernels = None
+    if rank == 0 and world == 1 and not args.no_kernels:
+        kernels = kernel_figures(ctx, jv, pk, quick=args.steps < 10)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(cfg, weights, x, min(args.cpu_layers, cfg.layers))
+
+    if rank == 0:
+        line = dict(
+            metric=METRIC, value=round(ms_step / world, 4), unit=UNIT, n_gpus=world, steps=args.steps, warmup=warmup,
+            ms_per_step=round(ms_step, 4), higher_is_better=False, scaling="weak", vs_baseline=None,
+            dtype="f16 (fp32 accumulate)", data="synthetic",
+            config=dict(workload=f"config 3: {cfg.layers}-layer pre-LN encoder, d_model {cfg.d_model}, {cfg.heads} heads, "
+                                 f"FFN {cfg.ffn} GELU, {cfg.tokens}x{cfg.d_model} input, batch 1 per GPU",
+                        parallelism=f"batch-sharded x{world}, weights replicated, no collective",
+                        l2="inputs larger than L2: each pass streams 1.18 GB of weights", replay="cuda graph",
+                        imgs_per_step=world, tflops_per_gpu=round(cfg.flops() / ms_step / 1e9, 1)),
+            e2e=dict(value=round(e2e_ms / world, 4), unit=UNIT, h2d_bytes_per_step=nbytes, d2h_bytes_per_step=nbytes),
+            gpu_launches=launches_per_pass * args.steps,
+            roofline=dict(bound="tensor", kernel="gemm_f16_tc_kernel", achieved=round(gemm_tflops, 1),
+                          peak=pk["tflops"], unit="TFLOP/s", frac=round(gemm_tflops / pk["tflops"], 4),
+                          peak_source=f"{pk['source']} (bf16 burst); spec dense fp16 2250",
+                          frac_of_spec=round(gemm_tflops / 2250.0, 4), launches=n_gemm,
+                          avg_launch_ms=round(gemm_ms / n_gemm, 5), traffic=None,
+                          note="all GEMM launches of one pass, replayed back to back; flops = 2MNK unpadded"),
+            clocks=clocks, kernels=kernels, cpu_baseline=cpu)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    _lib.lib().b200_host_free(hx)
+    _lib.lib().b200_host_free(hy)
+
+
+if __name__ == "__main__":
+    main()

@@ -78,6 +78,17 @@ int64_t b200_launch_count(b200_ctx* ctx);
 int b200_timer_start(b200_ctx* ctx);
 int b200_timer_stop(b200_ctx* ctx, float* ms_out); /* records, synchronises, reads */
 
+/* Capture / replay of a launch sequence (Lava capture / replay!, SAM2Runner/src/sam2.jl:90-115):
+ * everything launched on the context between begin and end is recorded into a CUDA graph
+ * instead of running; replay launches the whole sequence with one call.  The static slab and
+ * the warmed-up workspace make every device address repeat, which is the precondition.  Run
+ * the sequence once eagerly first: the pool must not need cudaMalloc while capturing. */
+typedef struct b200_graph b200_graph;
+int b200_graph_begin(b200_ctx* ctx);
+int b200_graph_end(b200_ctx* ctx, b200_graph** out);
+int b200_graph_launch(b200_ctx* ctx, b200_graph* g);
+int b200_graph_destroy(b200_graph* g);
+
 /* ------------------------------------- memory (Mantle pool / toback, driver.jl:81-115) */
 /* 256-byte aligned device block from the context's cudaMalloc pool (size-class free
  * lists; blocks return to the pool on free, to the driver on ctx destroy). */

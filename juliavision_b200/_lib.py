@@ -53,6 +53,10 @@ SIGNATURES = {
     "b200_launch_count": (_i64, [_vp]),
     "b200_timer_start": (_i32, [_vp]),
     "b200_timer_stop": (_i32, [_vp, C.POINTER(_f32)]),
+    "b200_graph_begin": (_i32, [_vp]),
+    "b200_graph_end": (_i32, [_vp, _pp]),
+    "b200_graph_launch": (_i32, [_vp, _vp]),
+    "b200_graph_destroy": (_i32, [_vp]),
     "b200_pool_alloc": (_i32, [_vp, _sz, _pp]),
     "b200_pool_free": (_i32, [_vp, _vp]),
     "b200_pool_stats": (_i32, [_vp, C.POINTER(_sz), C.POINTER(_sz)]),

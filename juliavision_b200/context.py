@@ -213,6 +213,15 @@ class Ctx:
             check(_lib.lib().b200_upload(self.handle, d.ptr, a.ctypes.data_as(C.c_void_p), a.nbytes))
         return d
 
+    def copy(self, dst: DeviceArray, src: DeviceArray) -> None:
+        """copyto!(dst, src) for two dense arrays of one size, asynchronous on the stream."""
+        assert dst.isdense() and src.isdense() and dst.nbytes == src.nbytes
+        check(_lib.lib().b200_copy(self.handle, dst.ptr, src.ptr, src.nbytes))
+
+    def upload(self, dst: DeviceArray, host: np.ndarray) -> None:
+        assert dst.isdense() and host.flags["C_CONTIGUOUS"] and dst.nbytes == host.nbytes
+        check(_lib.lib().b200_upload(self.handle, dst.ptr, host.ctypes.data_as(C.c_void_p), host.nbytes))
+
     def fill_bytes(self, a: DeviceArray, byte: int) -> None:
         assert a.isdense()
         check(_lib.lib().b200_fill_bytes(self.handle, a.ptr, byte, a.nbytes))
@@ -247,6 +256,38 @@ class Ctx:
     def scratch(self, dtype, *dims: int) -> DeviceArray:
         """scratch!(ctx, T, dims...) (workspace.jl:105)."""
         return self.ws.scratch(dtype, *dims)
+
+    # -- capture / replay (the reference's Lava capture + replay!, SAM2Runner/src/sam2.jl:90-115)
+    def capture(self, fn) -> "Graph":
+        """Record everything `fn()` launches on this context into a graph.  Call `fn()` once
+        eagerly beforehand so the pool and workspace need no new memory while recording."""
+        check(_lib.lib().b200_graph_begin(self.handle))
+        try:
+            fn()
+        except BaseException:
+            g = C.c_void_p()
+            _lib.lib().b200_graph_end(self.handle, C.byref(g))
+            if g.value:
+                _lib.lib().b200_graph_destroy(g)
+            raise
+        g = C.c_void_p()
+        check(_lib.lib().b200_graph_end(self.handle, C.byref(g)))
+        return Graph(self, g.value)
+
+
+class Graph:
+    def __init__(self, ctx: "Ctx", handle: int):
+        self.ctx, self.handle = ctx, handle
+
+    def replay(self) -> None:
+        check(_lib.lib().b200_graph_launch(self.ctx.handle, self.handle))
+
+    def __del__(self):
+        try:
+            if self.handle:
+                _lib.lib().b200_graph_destroy(self.handle)
+        except Exception:
+            pass
 
 
 def caps(ctx: Ctx) -> DeviceCaps:

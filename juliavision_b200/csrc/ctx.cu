@@ -43,6 +43,9 @@ int pool_alloc(b200_ctx* ctx, size_t bytes, void** out) {
         ctx->free_blocks.erase(it);
         return B200_OK;
     }
+    if (ctx->capturing)
+        return fail(B200_ENOMEM, "pool: %zu bytes needed while capturing a graph; run the sequence once eagerly "
+                                 "so the pool and workspace are warm", need);
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, need);
     if (e != cudaSuccess) {
@@ -225,6 +228,42 @@ int b200_timer_stop(b200_ctx* c, float* ms) {
     B200_CUDA(cudaEventRecord(c->ev1, c->stream));
     B200_CUDA(cudaEventSynchronize(c->ev1));
     B200_CUDA(cudaEventElapsedTime(ms, c->ev0, c->ev1));
+    return B200_OK;
+}
+
+int b200_graph_begin(b200_ctx* c) {
+    B200_REQUIRE(c, B200_EINVAL, "graph_begin: null ctx");
+    B200_REQUIRE(!c->capturing, B200_EINVAL, "graph_begin: already capturing");
+    B200_CUDA(cudaSetDevice(c->device));
+    B200_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    c->capturing = true;
+    return B200_OK;
+}
+int b200_graph_end(b200_ctx* c, b200_graph** out) {
+    B200_REQUIRE(c && out, B200_EINVAL, "graph_end: null argument");
+    B200_REQUIRE(c->capturing, B200_EINVAL, "graph_end: not capturing");
+    c->capturing = false;
+    cudaGraph_t g = nullptr;
+    B200_CUDA(cudaStreamEndCapture(c->stream, &g));
+    cudaGraphExec_t ex = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&ex, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGraphInstantiate");
+    b200_graph* r = new b200_graph();
+    r->exec = ex;
+    *out = r;
+    return B200_OK;
+}
+int b200_graph_launch(b200_ctx* c, b200_graph* g) {
+    B200_REQUIRE(c && g && g->exec, B200_EINVAL, "graph_launch: null argument");
+    B200_CUDA(cudaGraphLaunch(g->exec, c->stream));
+    return B200_OK;
+}
+int b200_graph_destroy(b200_graph* g) {
+    if (g) {
+        if (g->exec) cudaGraphExecDestroy(g->exec);
+        delete g;
+    }
     return B200_OK;
 }
 

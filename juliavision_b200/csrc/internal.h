@@ -46,6 +46,7 @@ struct b200_ctx {
     cudaDeviceProp prop{};
     int* d_status = nullptr;   // device status words: [0] first failed wait code
     int64_t launches = 0;
+    bool capturing = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     b200::EncodeTiledFn encode = nullptr;
 
@@ -59,6 +60,10 @@ struct b200_ctx {
     void* ws_buf = nullptr;
     size_t ws_cap = 0, ws_used = 0;
     std::vector<b200::RetiredBlock> ws_retired;
+};
+
+struct b200_graph {
+    cudaGraphExec_t exec = nullptr;
 };
 
 namespace b200 {

@@ -1,0 +1,53 @@
+import numpy as np
+import pytest
+
+import juliavision_b200 as jv
+from juliavision_b200.encoder import Encoder, EncoderConfig, init_weights
+
+from .conftest import relerr
+from .gpu_helpers import describe
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(ctx, cfg, x, graph=False):
+    w = init_weights(cfg)
+    enc = Encoder(ctx, cfg, w)
+    ctx.upload(enc.xin, x)
+    if graph:
+        g = enc.capture()
+        ctx.fill_bytes(enc.y, 0xFF)
+        g.replay()
+    else:
+        enc.forward()
+    ctx.synchronize()
+    return enc, w, enc.y.to_host()
+
+
+def test_two_layer_prefix_vs_oracle(ctx):
+    """The reference verifies a 2-block prefix on its CPU backend (verify.jl:115-118); so does this."""
+    from oracle.encoder_ref import oracle_forward
+    cfg = EncoderConfig(layers=2, d_model=256, heads=4, ffn=1024, tokens=300)
+    x = np.float16(np.random.default_rng(1).standard_normal((cfg.tokens, cfg.d_model)))
+    enc, w, got = _run(ctx, cfg, x)
+    ref = oracle_forward(cfg, w, x)
+    assert got.shape == (cfg.tokens, cfg.d_model)
+    assert relerr(got, ref) < 1e-2, describe(got, ref, 1e-2)
+
+
+def test_graph_replay_equals_eager(ctx):
+    cfg = EncoderConfig(layers=3, d_model=128, heads=2, ffn=512, tokens=200)
+    x = np.float16(np.random.default_rng(2).standard_normal((cfg.tokens, cfg.d_model)))
+    _, _, eager = _run(ctx, cfg, x, graph=False)
+    _, _, replay = _run(ctx, cfg, x, graph=True)
+    assert np.array_equal(eager, replay)
+
+
+def test_config3_shape_one_layer_vs_oracle(ctx):
+    """Config-3 geometry (d 1280, 20 heads of 64, FFN 5120, 1500 tokens), one layer of the 32."""
+    from oracle.encoder_ref import oracle_forward
+    cfg = EncoderConfig(layers=1)
+    x = np.float16(np.random.default_rng(3).standard_normal((cfg.tokens, cfg.d_model)))
+    enc, w, got = _run(ctx, cfg, x)
+    ref = oracle_forward(cfg, w, x)
+    assert relerr(got, ref) < 1e-2, describe(got, ref, 1e-2)

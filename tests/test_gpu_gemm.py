@@ -1,0 +1,136 @@
+import os
+
+import numpy as np
+import pytest
+
+import juliavision_b200 as jv
+
+from .conftest import relerr
+from .gpu_helpers import describe, linear_gpu
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+TOL = 1e-2  # max relative error on fp16 outputs against the fp32-accumulated oracle
+
+
+def test_golden(ctx):
+    g = np.load(os.path.join(G, "linear.npz"))
+    for epi, key in (("identity", "y_none"), ("gelu", "y_gelu"), ("relu", "y_relu")):
+        got = linear_gpu(ctx, g["X"], g["Wt"], g["b"], epi=epi)
+        assert got.shape == g[key].shape
+        assert relerr(got, g[key]) < 2e-3, (epi, describe(got, g[key], 2e-3))
+
+
+def _case(rng, tokens, out, K, scale=0.05):
+    X = (rng.standard_normal((tokens, K)) * scale).astype(np.float16)
+    Wt = (rng.standard_normal((K, out)) * scale).astype(np.float16)
+    b = (rng.standard_normal(out) * scale).astype(np.float16)
+    return X, Wt, b
+
+
+# (tokens, out features, K): aligned, ragged tokens, ragged features, ragged K, tiny, one tile each way
+SHAPES = [(256, 256, 128), (128, 64, 64), (1500, 1280, 1280), (100, 1000, 768), (37, 40, 72), (300, 3072, 768),
+          (129, 264, 200), (1, 8, 8), (513, 520, 1032), (2000, 112, 448)]
+
+
+@pytest.mark.parametrize("tokens,out,K", SHAPES)
+def test_vs_oracle(ctx, ora, tokens, out, K):
+    rng = np.random.default_rng(tokens * 7 + out * 3 + K)
+    X, Wt, b = _case(rng, tokens, out, K, scale=0.25)
+    plan = jv.mmplan(ctx, ctx.allocate(np.float16, out, tokens), ctx.toback(Wt), ctx.toback(X))
+    assert isinstance(plan, jv.MMTilePlan), plan
+    for epi, bias in (("identity", b), ("gelu", b), ("relu", None)):
+        got = linear_gpu(ctx, X, Wt, bias, epi=epi)
+        ref = ora.linear(X, Wt, bias, epi=epi if epi != "identity" else "none")
+        assert got.shape == (tokens, out)
+        assert relerr(got, ref) < TOL, (epi, describe(got, ref, TOL))
+        # tighter: the only differences are fp32 summation order, i.e. a last-bit flip here and there
+        d = np.abs(got.astype(np.float64) - ref.astype(np.float64))
+        assert np.mean(d > 4 * np.spacing(np.abs(ref)).astype(np.float64) + 1e-6) < 1e-3
+
+
+def test_config1_linear(ctx, ora):
+    """BASELINE config 1: X 4096x768, W 3072x768, b 3072, N(0,1)*0.05, fp16 out."""
+    rng = np.random.default_rng(20260101)
+    X, Wt, b = _case(rng, 4096, 3072, 768)
+    got = linear_gpu(ctx, X, Wt, b)
+    ref = ora.linear(X, Wt, b)
+    assert relerr(got, ref) < TOL, describe(got, ref, TOL)
+
+
+def test_fp32_output(ctx, ora):
+    rng = np.random.default_rng(5)
+    X, Wt, b = _case(rng, 200, 136, 264, scale=0.25)
+    got = linear_gpu(ctx, X, Wt, b, epi="gelu", out_dtype=np.float32)
+    ref = ora.linear(X, Wt, b, epi="gelu", out_dtype=np.float32)
+    assert got.dtype == np.float32
+    assert relerr(got, ref) < 1e-4, describe(got, ref, 1e-4)
+
+
+def test_unaligned_operands_take_the_scalar_kernel_bit_exact(ctx, ora):
+    """lda = 37 cannot be a tensor-map stride: the scalar kernel runs mm2's arithmetic, so the
+    result equals the oracle bit for bit."""
+    rng = np.random.default_rng(6)
+    X, Wt, b = _case(rng, 50, 37, 96, scale=0.25)
+    plan = jv.mmplan(ctx, ctx.allocate(np.float16, 37, 50), ctx.toback(Wt), ctx.toback(X))
+    assert isinstance(plan, jv.MMScalarPlan)
+    got = linear_gpu(ctx, X, Wt, b, epi="relu")
+    assert np.array_equal(got, ora.linear(X, Wt, b, epi="relu"))
+
+
+def test_batched(ctx, ora):
+    rng = np.random.default_rng(7)
+    nb, m, k, n = 6, 70, 64, 136
+    a = (rng.standard_normal((nb, m, k)) * 0.25).astype(np.float16)
+    b = (rng.standard_normal((nb, k, n)) * 0.25).astype(np.float16)
+    A, B = ctx.toback(b), ctx.toback(a)          # reference orientation: A = torch b (n,k,nb), B = torch a (k,m,nb)
+    out = ctx.allocate(np.float16, n, m, nb)
+    ctx.fill_bytes(out, 0xFF)
+    jv.batchedmatmul_(ctx, out, A, B)
+    ctx.synchronize()
+    got = out.to_host()
+    ref = ora.bmm(a, b)
+    assert relerr(got, ref) < TOL, describe(got, ref, TOL)
+
+
+def test_padded_leading_dimensions(ctx, ora):
+    """Views into wider buffers (ld > extent): the bytes outside the view stay untouched."""
+    rng = np.random.default_rng(8)
+    tokens, out, K = 130, 72, 80
+    X, Wt, b = _case(rng, tokens, out, K, scale=0.25)
+    big = ctx.allocate(np.float16, 96, tokens)
+    ctx.fill_bytes(big, 0xFF)
+    view = big.slice(0, 0, out)                   # (72, tokens) with ld 96
+    jv.matmul_(ctx, view, ctx.toback(Wt), ctx.toback(X), ctx.toback(b))
+    ctx.synchronize()
+    host = big.to_host()                          # torch (tokens, 96)
+    assert relerr(host[:, :out], ora.linear(X, Wt, b)) < TOL
+    assert np.all(np.isnan(host[:, out:]))
+
+
+def test_declines(ctx):
+    a32 = ctx.allocate(np.float32, 64, 64)
+    a16 = ctx.allocate(np.float16, 64, 64)
+    assert jv.mmplan(ctx, a16, a32, a16) == jv.Decline("operands")       # test_batchedmatmul.jl:107-125
+    assert jv.mmplan(ctx, a16, a16, ctx.allocate(np.float16, 32, 64)) == jv.Decline("extent")
+    with pytest.raises(jv.B200Error):
+        jv.matmul_(ctx, a16, a32, a16)
+    empty = ctx.allocate(np.float16, 64, 0)
+    assert jv.mmplan(ctx, empty, a16, empty) == jv.Decline("extent")
+
+
+def test_linearity_at_full_size(ctx):
+    """Size-independent property at the bench's size: W = [I;0] copies X, and f(X1+X2) = f(X1)+f(X2)
+    for operands whose sums are exact in fp16."""
+    tokens, K, out = 4096, 768, 3072
+    rng = np.random.default_rng(9)
+    X = rng.integers(-8, 9, (tokens, K)).astype(np.float16)
+    Wt = np.zeros((K, out), np.float16)
+    Wt[np.arange(K), np.arange(K)] = 1
+    got = linear_gpu(ctx, X, Wt)
+    assert np.array_equal(got[:, :K], X) and not got[:, K:].any()
+    W2 = rng.integers(-2, 3, (K, out)).astype(np.float16)
+    X2 = rng.integers(-2, 3, (tokens, K)).astype(np.float16)
+    X1 = rng.integers(-2, 3, (tokens, K)).astype(np.float16)
+    y1, y2, y12 = (linear_gpu(ctx, x, W2, out_dtype=np.float32) for x in (X1, X2, X1 + X2))
+    assert np.array_equal(y1 + y2, y12)           # integer-valued: every partial sum is exact
