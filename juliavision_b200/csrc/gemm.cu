@@ -212,8 +212,9 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             const float rbias =
                 (p.bias != nullptr && p.bias_per_n && n0 + row < p.N) ? __half2float(p.bias[n0 + row]) : 0.f;
             const bool got = mbar_wait(&tfull[acc], aph, p.d_status, KST_WAIT_TMEM_FULL, abort_flag);
-            named_bar_sync(1, 128);
-            if (!got || *abort_flag) break;
+            // One answer for all 128 threads: a split decision would strand the rest at the
+            // barriers inside the chunk loop.
+            if (named_bar_or(1, 128, !got || *abort_flag != 0)) break;
             tc_fence_after();
 
             constexpr int NCHUNK = BN / Cfg::OUT_COLS;

@@ -161,6 +161,23 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Named barrier that also ORs a predicate across its participants: every thread gets the same
+// answer, so a "leave the loop" decision taken on it can never split the group.
+__device__ __forceinline__ bool named_bar_or(int id, int nthreads, bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P, Q;\n\t"
+        "setp.ne.b32 Q, %3, 0;\n\t"
+        "bar.red.or.pred P, %1, %2, Q;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(out)
+        : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+        : "memory");
+    return out != 0;
+}
+
 // ------------------------------------------------------------------------- tcgen05
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(

@@ -1,0 +1,234 @@
+# B200Backend.jl — the reference-side binding of libb200dnn.so.
+#
+# Drop this file into DNNKernels/src and `include("B200Backend.jl")` after kernelplans.jl.
+# It adds a backend, a device array, the caps answer, new plan types and one method per
+# entry point (`matmul!`, `sdpa!`, `layernorm!`, `convolution!`, `scratch!`, `toback`), which is
+# the extension rule the package states: a new path is a new plan type plus a new method
+# (kernels/extern/matmul.jl:97-100, kernels/extern/attention.jl:767-771, kernelplans.jl:1-19).
+# Nothing else in the package changes: `execute!`, the rewrite passes, `planslab` and `dest`
+# keep working because `B200Array` is a dense column-major array like `LavaArray`.
+#
+# No Julia toolchain exists where this file was written, so it has not been executed; the
+# identical call sequence is exercised through the same C symbols by the Python mirror in
+# juliavision_b200/*.py and its tests.
+
+module B200
+
+using ..DNNKernels: Ctx, Decline, accum, actfn, geluexact, gelutanh, relu_epi
+import ..DNNKernels: matmul!, mmplan, batchedmatmul!, sdpa!, sdpaplan, layernorm!, convolution!,
+                     scratch!, toback, caps, slabview
+import KernelAbstractions
+
+const LIB = get(ENV, "B200DNN_LIB", "libb200dnn.so")
+
+# ------------------------------------------------------------------ status handling
+const OK = Cint(0)
+const DECLINE = Dict(16 => :operands, 17 => :extent, 18 => :wrapped, 19 => :bias, 20 => :eltype, 21 => :tiling)
+lasterror() = unsafe_string(ccall((:b200_last_error, LIB), Cstring, ()))
+check(rc::Cint) = rc == OK ? nothing : error("b200dnn status $rc: $(lasterror())")
+
+# ------------------------------------------------------------------ backend / arrays
+mutable struct B200Backend <: KernelAbstractions.GPU
+    handle::Ptr{Cvoid}
+    device::Int
+    function B200Backend(device::Integer = 0)
+        h = Ref{Ptr{Cvoid}}(C_NULL)
+        check(ccall((:b200_ctx_create, LIB), Cint, (Cint, Ref{Ptr{Cvoid}}), device, h))
+        b = new(h[], device)
+        finalizer(x -> ccall((:b200_ctx_destroy, LIB), Cint, (Ptr{Cvoid},), x.handle), b)
+    end
+end
+
+"""Dense column-major device array; `parent` keeps the pool block or slab alive."""
+struct B200Array{T,N} <: DenseArray{T,N}
+    ptr::Ptr{T}
+    dims::NTuple{N,Int}
+    backend::B200Backend
+    parent::Any
+end
+Base.size(a::B200Array) = a.dims
+Base.pointer(a::B200Array) = a.ptr
+Base.strides(a::B200Array) = Base.size_to_strides(1, a.dims...)
+KernelAbstractions.get_backend(a::B200Array) = a.backend
+KernelAbstractions.synchronize(b::B200Backend) = check(ccall((:b200_sync, LIB), Cint, (Ptr{Cvoid},), b.handle))
+
+mutable struct PoolBlock
+    backend::B200Backend
+    ptr::Ptr{Cvoid}
+end
+function KernelAbstractions.allocate(b::B200Backend, ::Type{T}, dims::Integer...) where {T}
+    p = Ref{Ptr{Cvoid}}(C_NULL)
+    check(ccall((:b200_pool_alloc, LIB), Cint, (Ptr{Cvoid}, Csize_t, Ref{Ptr{Cvoid}}), b.handle,
+                max(prod(dims), 1) * sizeof(T), p))
+    blk = PoolBlock(b, p[])
+    finalizer(x -> ccall((:b200_pool_free, LIB), Cint, (Ptr{Cvoid}, Ptr{Cvoid}), x.backend.handle, x.ptr), blk)
+    B200Array{T,length(dims)}(Ptr{T}(p[]), Int.(dims), b, blk)
+end
+
+"""`toback(backend, a)` (driver.jl:108-115): upload a host array."""
+function toback(b::B200Backend, a::AbstractArray{T}) where {T}
+    h = Array(a)
+    d = KernelAbstractions.allocate(b, T, size(h)...)
+    check(ccall((:b200_upload, LIB), Cint, (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Csize_t), b.handle, d.ptr, h,
+                sizeof(h)))
+    d
+end
+function Base.Array(a::B200Array{T,N}) where {T,N}
+    h = Array{T,N}(undef, a.dims)
+    check(ccall((:b200_download, LIB), Cint, (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Csize_t), a.backend.handle, h,
+                a.ptr, sizeof(h)))
+    h
+end
+
+"""`slabview(T, slab, dims, off)` (execute.jl:173-179): a typed view at a byte offset of a slab."""
+slabview(::Type{T}, slab::B200Array{UInt8,1}, dims, off::Integer) where {T} =
+    B200Array{T,length(dims)}(Ptr{T}(slab.ptr + off), Int.(Tuple(dims)), slab.backend, slab)
+
+"""`scratch!(ws, backend, T, dims...)` (workspace.jl:63-96) served by the library's bump workspace."""
+function scratch!(::Any, b::B200Backend, ::Type{T}, dims::Integer...) where {T}
+    p = Ref{Ptr{Cvoid}}(C_NULL)
+    check(ccall((:b200_workspace_scratch, LIB), Cint, (Ptr{Cvoid}, Csize_t, Ref{Ptr{Cvoid}}), b.handle,
+                prod(dims) * sizeof(T), p))
+    B200Array{T,length(dims)}(Ptr{T}(p[]), Int.(dims), b, nothing)
+end
+resetworkspace!(b::B200Backend) = check(ccall((:b200_workspace_reset, LIB), Cint, (Ptr{Cvoid},), b.handle))
+
+# ------------------------------------------------------------------ caps (context.jl:55-68)
+struct CapsC
+    coopmat::Int32; tile::Int32; subgroup::Int32; coopmatsubgroup::Int32; sharedbudget::Int32
+    workgrouplimit::Int32; cores::Int32; warps::Int32; cc_major::Int32; cc_minor::Int32; total_mem::Int64
+end
+struct B200Caps
+    coopmat::Bool; tile::Int; subgroup::Int; coopmatsubgroup::Int; sharedbudget::Int
+    workgrouplimit::Int; cores::Int; warps::Int
+end
+function caps(b::B200Backend)
+    c = Ref{CapsC}()
+    check(ccall((:b200_caps, LIB), Cint, (Ptr{Cvoid}, Ref{CapsC}), b.handle, c))
+    B200Caps(c[].coopmat != 0, c[].tile, c[].subgroup, c[].coopmatsubgroup, c[].sharedbudget,
+             c[].workgrouplimit, c[].cores, c[].warps)
+end
+
+# ------------------------------------------------------------------ plans
+"""Tensor-core GEMM plan; no padded extent — ragged M/N/K are TMA-clipped tiles."""
+struct MMTilePlan end
+"""fp16 operands a tensor map cannot express: the scalar kernel (mm2's arithmetic) on the GPU."""
+struct MMScalarPlan end
+"""Fused single-pass attention on tcgen05."""
+struct FlashTCPlan end
+struct AttnScalarPlan end
+
+dtcode(::Type{Float16}) = Cint(0)
+dtcode(::Type{Float32}) = Cint(1)
+epicode(epi) = epi === geluexact ? Cint(2) : epi === relu_epi ? Cint(1) : epi === gelutanh ? Cint(3) :
+               epi === identity ? Cint(0) : error("no fused form for epilogue $epi")
+
+"""Root pointer + strides of a wrapper stack over a B200Array (the job of `stridedroot`,
+attention.jl:321-337): `nothing` when the stack is not a strided view."""
+function rootstrides(a)
+    a isa B200Array && return (pointer(a), strides(a))
+    try
+        return (pointer(a), strides(a))     # SubArray / PermutedDimsArray / ReshapedArray of dense parents
+    catch
+        return nothing
+    end
+end
+
+# ------------------------------------------------------------------ matmul! (matmul.jl:78-100)
+function mmplan(dev::B200Caps, out, A, B, bias)
+    eltype(A) === Float16 && eltype(B) === Float16 || return Decline(:operands)
+    eltype(out) in (Float16, Float32) || return Decline(:eltype)
+    ra, rb, ro = rootstrides(A), rootstrides(B), rootstrides(out)
+    (ra === nothing || rb === nothing || ro === nothing) && return Decline(:wrapped)
+    (ra[2][1] == 1 && rb[2][1] == 1 && ro[2][1] == 1) || return Decline(:wrapped)
+    M, K = size(A); N = size(B, 2)
+    rc = ccall((:b200_gemm_f16_supported, LIB), Cint, (Int64, Int64, Int64, Int64, Int64, Int64, Cint),
+               M, N, K, ra[2][2], rb[2][2], ro[2][2], dtcode(eltype(out)))
+    rc == OK && return MMTilePlan()
+    rc == 18 && return MMScalarPlan()
+    Decline(get(DECLINE, Int(rc), :extent))
+end
+
+function matmul!(ctx, ::Union{MMTilePlan,MMScalarPlan}, out, A, B, bias, epi; gemm = NamedTuple())
+    M, K = size(A); N = size(B, 2)
+    check(ccall((:b200_gemm_f16, LIB), Cint,
+                (Ptr{Cvoid}, Int64, Int64, Int64, Ptr{Cvoid}, Int64, Ptr{Cvoid}, Int64, Ptr{Cvoid}, Ptr{Cvoid},
+                 Int64, Cint, Cint, Int64, Int64, Int64, Int64),
+                ctx.backend.handle, M, N, K, pointer(A), stride(A, 2), pointer(B), stride(B, 2),
+                bias === nothing ? C_NULL : pointer(bias), pointer(out), stride(out, 2), dtcode(eltype(out)),
+                epicode(epi), 1, 0, 0, 0))
+    out
+end
+# No CPU path behind this backend: a refusal is an error, not a slower route.
+matmul!(ctx::Ctx{B200Backend}, d::Decline, out, A, B, bias, epi; gemm = NamedTuple()) =
+    error("matmul!: Decline(:$(d.reason)) on the B200 backend")
+
+function batchedmatmul!(ctx::Ctx{B200Backend}, out, A, B)
+    M, K, nb = size(A); N = size(B, 2)
+    check(ccall((:b200_gemm_f16, LIB), Cint,
+                (Ptr{Cvoid}, Int64, Int64, Int64, Ptr{Cvoid}, Int64, Ptr{Cvoid}, Int64, Ptr{Cvoid}, Ptr{Cvoid},
+                 Int64, Cint, Cint, Int64, Int64, Int64, Int64),
+                ctx.backend.handle, M, N, K, pointer(A), stride(A, 2), pointer(B), stride(B, 2), C_NULL,
+                pointer(out), stride(out, 2), dtcode(eltype(out)), 0, nb, stride(A, 3), stride(B, 3),
+                stride(out, 3)))
+    out
+end
+
+# ------------------------------------------------------------------ sdpa! (attention.jl:712-834)
+struct Strided4
+    ptr::Ptr{Cvoid}
+    stride::NTuple{4,Int64}
+end
+s4(a) = (r = rootstrides(a); Strided4(Ptr{Cvoid}(r[1]), Int64.(r[2])))
+
+function sdpaplan(ctx::Ctx{B200Backend}, q, k, v, bias)
+    bias === nothing || return (Decline(:bias), k, v)
+    all(x -> eltype(x) === Float16, (q, k, v)) || return (Decline(:eltype), k, v)
+    any(x -> rootstrides(x) === nothing, (q, k, v)) && return (Decline(:wrapped), k, v)
+    E, Lq, H, B = size(q); Lk = size(k, 2)
+    st(x) = collect(Int64.(rootstrides(x)[2]))
+    rc = ccall((:b200_attention_f16_supported, LIB), Cint,
+               (Int64, Int64, Int64, Int64, Int64, Ptr{Int64}, Ptr{Int64}, Ptr{Int64}, Cint),
+               E, Lq, Lk, H, B, st(q), st(k), st(v), 0)
+    rc == OK && return (FlashTCPlan(), k, v)
+    rc in (18, 21) && return (AttnScalarPlan(), k, v)
+    (Decline(get(DECLINE, Int(rc), :extent)), k, v)
+end
+
+function sdpa!(ctx, ::Union{FlashTCPlan,AttnScalarPlan}, out, q, k, v, bias, scale)
+    E, Lq, H, B = size(q); Lk = size(k, 2)
+    out === nothing && (out = KernelAbstractions.allocate(ctx.backend, accum(eltype(q)), E, Lq, H, B))
+    check(ccall((:b200_attention_f16, LIB), Cint,
+                (Ptr{Cvoid}, Int64, Int64, Int64, Int64, Int64, Ref{Strided4}, Ref{Strided4}, Ref{Strided4},
+                 Ptr{Cvoid}, Cint, Cfloat),
+                ctx.backend.handle, E, Lq, Lk, H, B, s4(q), s4(k), s4(v), pointer(out), dtcode(eltype(out)),
+                Float32(scale)))
+    out
+end
+
+# ------------------------------------------------------------------ layernorm! (layernorm.jl:125-135)
+function layernorm!(ctx::Ctx{B200Backend}, out, mean, rstd, a, γ, β, C::Integer, eps::Real)
+    groups = length(a) ÷ C
+    check(ccall((:b200_layernorm, LIB), Cint,
+                (Ptr{Cvoid}, Int64, Int64, Ptr{Cvoid}, Cint, Ptr{Cvoid}, Cint, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
+                 Ptr{Cvoid}, Cfloat),
+                ctx.backend.handle, groups, C, pointer(a), dtcode(eltype(a)), pointer(out), dtcode(eltype(out)),
+                pointer(mean), pointer(rstd), γ === nothing ? C_NULL : pointer(γ),
+                β === nothing ? C_NULL : pointer(β), Float32(eps)))
+    out
+end
+
+# ------------------------------------------------------------------ convolution! (conv.jl:100-145)
+function convolution!(ctx::Ctx{B200Backend}, out, x, w, bias, stride, padding, dilation, groups; act = :none)
+    groups == 1 || error("convolution!: Decline(:groups) on the B200 backend")
+    W, H, Cin, N = size(x); KW, KH, _, Cout = size(w)
+    check(ccall((:b200_conv2d_f16, LIB), Cint,
+                (Ptr{Cvoid}, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64,
+                 Int64, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Cint, Cint),
+                ctx.backend.handle, W, H, Cin, N, KW, KH, Cout, stride[1], stride[2], padding[1], padding[2],
+                dilation[1], dilation[2], pointer(x), pointer(w), bias === nothing ? C_NULL : pointer(bias),
+                pointer(out), dtcode(eltype(out)), act === :relu ? 1 : act === :gelu ? 2 : 0))
+    out
+end
+
+end # module
