@@ -194,6 +194,30 @@ int b200_conv2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N,
                     int64_t dx, int64_t dy, const void* x, const void* w, const void* bias,
                     void* out, int out_dtype, int epilogue);
 
+/*
+ * The same convolution for callers that must not allocate device memory when they call: a
+ * server whose own allocator took the whole GPU at start-up, or a loop that may not make a
+ * device-synchronising call such as cudaMalloc/cudaFree.  (No counterpart in the reference;
+ * b200_conv2d_f16 above is the entry point that replaces the reference's convolution.)
+ * The im2col matrix and the padded weight live in a fixed 32 MiB array built into the library
+ * (each GPU that loads the library holds it until the process exits) instead of the workspace,
+ * and the call makes no cudaMalloc, cudaFree or other allocating call.  Same arguments and
+ * results as b200_conv2d_f16.
+ *   - Limit: padded weight (only when KW*KH*Cin is not a multiple of 8: roundup8(KW*KH*Cin)*Cout*2
+ *     bytes, rounded up to 256) + im2col matrix (only when not 1x1/stride 1/no padding:
+ *     roundup8(OW*OH)*KW*KH*Cin*2 bytes) must fit in 32 MiB; otherwise B200_ENOMEM with the sizes
+ *     in b200_last_error().  The 1024x1024x3, 7x7 stride-4 stem needs 19.3 MB.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress);
+ *     make that first call before starting any stream capture.
+ *   - All calls on a GPU share the one array and it keeps the previous call's bytes.  Each call
+ *     rewrites every byte it later reads, so stale contents are harmless, but two calls whose
+ *     kernels overlap on the GPU (different contexts/streams on one device) race on it.
+ */
+int b200_conv2d_f16_noalloc(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW,
+                            int64_t KH, int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py,
+                            int64_t dx, int64_t dy, const void* x, const void* w, const void* bias,
+                            void* out, int out_dtype, int epilogue);
+
 /* ------------------------------------------- encoder glue ops (bandwidth-bound) */
 /* add.Tensor, clamp.default, gelu.default on fp16 (ops.jl:186-197,323-335,1698-1702). */
 int b200_add_f16(b200_ctx* ctx, const void* a, const void* b, void* out, int64_t n);

@@ -142,4 +142,96 @@ int b200_conv2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N,
     return B200_OK;
 }
 
+
+// ---------------------------------------------------------------- no-allocation variant
+//
+// Some hosts of this library may not allocate device memory at call time: a serving process
+// whose own allocator claimed the whole GPU at start-up (a cudaMalloc from a plug-in then fails
+// or fragments its arena), or a latency-critical loop whose rules forbid calls that synchronise
+// the device, which cudaMalloc and cudaFree do.  b200_conv2d_f16 takes its im2col matrix and
+// padded weight from the context's workspace, which grows through cudaMalloc.  The variant
+// below takes them from a fixed array that is part of the loaded module instead, so it never
+// allocates: every GPU that loads the library carries these B200_NOALLOC_SCRATCH_BYTES until the
+// process exits.
+//
+// `g_noalloc_scratch` names a device symbol.  In host code that name is only a handle for the
+// runtime, not an address a kernel can use, so the device address is looked up once per device
+// with cudaGetSymbolAddress (that device current) and cached; kernels and tensor maps only ever
+// see the looked-up pointer.
+#define B200_NOALLOC_SCRATCH_BYTES (32u << 20)
+static __device__ __align__(256) unsigned char g_noalloc_scratch[B200_NOALLOC_SCRATCH_BYTES];
+static void* g_noalloc_addr[64] = {};
+
+static int noalloc_scratch(b200_ctx* ctx, void** out) {
+    const int dev = ctx->device;
+    if (dev < 0 || dev >= 64) return fail(B200_EINVAL, "conv2d_noalloc: device index %d", dev);
+    if (!g_noalloc_addr[dev]) {
+        B200_CUDA(cudaSetDevice(dev));
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
+        if (!p) return fail(B200_ECUDA, "conv2d_noalloc: the scratch symbol has no address on device %d", dev);
+        g_noalloc_addr[dev] = p;
+    }
+    *out = g_noalloc_addr[dev];
+    return B200_OK;
+}
+
+int b200_conv2d_f16_noalloc(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW, int64_t KH,
+                            int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py, int64_t dx, int64_t dy,
+                            const void* x, const void* w, const void* bias, void* out, int out_dtype,
+                            int epilogue) {
+    B200_REQUIRE(ctx && x && w && out, B200_EINVAL, "conv2d_noalloc: null argument");
+    B200_REQUIRE(W > 0 && H > 0 && Cin > 0 && N > 0 && KW > 0 && KH > 0 && Cout > 0 && sx > 0 && sy > 0 &&
+                     dx > 0 && dy > 0 && px >= 0 && py >= 0,
+                 B200_EINVAL, "conv2d_noalloc: bad geometry");
+    const int64_t OW = convsize(W, KW, sx, px, dx), OH = convsize(H, KH, sy, py, dy);
+    B200_REQUIRE(OW > 0 && OH > 0, B200_DECLINE_EXTENT, "conv2d_noalloc: empty output");
+    const int64_t P = OW * OH, CRS = KW * KH * Cin;
+    const size_t osz = out_dtype == B200_F16 ? 2 : 4;
+    const bool onebyone = KW == 1 && KH == 1 && sx == 1 && sy == 1 && px == 0 && py == 0;
+    const int64_t ldw = (CRS + 7) / 8 * 8, MP = (P + 7) / 8 * 8;
+    // Carve-up of the fixed array: [padded weight | im2col matrix], each 256-byte aligned.
+    const size_t wbytes = CRS % 8 != 0 ? ((size_t)(ldw * Cout) * 2 + 255) / 256 * 256 : 0;
+    const size_t cbytes = onebyone ? 0 : (size_t)(MP * CRS) * 2;
+    if (wbytes + cbytes > B200_NOALLOC_SCRATCH_BYTES)
+        return fail(B200_ENOMEM,
+                    "conv2d_noalloc: this convolution needs %zu bytes of scratch (padded weight %zu + im2col %zu) "
+                    "but the built-in array holds %u; use b200_conv2d_f16, which draws on the workspace",
+                    wbytes + cbytes, wbytes, cbytes, (unsigned)B200_NOALLOC_SCRATCH_BYTES);
+    B200_CUDA(cudaSetDevice(ctx->device));
+    void* base = nullptr;
+    int rc = noalloc_scratch(ctx, &base);
+    if (rc) return rc;
+
+    const void* wB = w;
+    int64_t ldwB = CRS;
+    if (wbytes) {
+        // Every element of the padded weight is written (the zero rows too), so nothing a
+        // previous call left in the array can leak into this one.
+        padrows_f16_kernel<<<grid_for(ctx, ldw * Cout), 256, 0, ctx->stream>>>((__half*)base, (const __half*)w,
+                                                                                (int)CRS, (int)ldw, ldw * Cout);
+        ctx->launches++;
+        B200_CUDA(cudaGetLastError());
+        wB = base;
+        ldwB = ldw;
+    }
+    void* col = (char*)base + wbytes;
+    for (int64_t n = 0; n < N; ++n) {
+        void* on = (char*)out + (size_t)(n * P * Cout) * osz;
+        if (onebyone) {
+            const __half* xa = (const __half*)x + n * P * Cin;
+            if ((rc = gemm_f16_run(ctx, P, Cout, Cin, xa, P, wB, ldwB, bias, 1, on, P, out_dtype, epilogue, 1, 0, 0, 0)))
+                return rc;
+            continue;
+        }
+        // The gather writes all MP x CRS entries, zeros included: no clearing pass is needed.
+        const __half* xn = (const __half*)x + n * W * H * Cin;
+        if ((rc = b200_im2col_f16(ctx, W, H, Cin, 1, KW, KH, sx, sy, px, py, dx, dy, MP, CRS, xn, col))) return rc;
+        if ((rc = gemm_f16_run(ctx, P, Cout, CRS, col, MP, wB, ldwB, bias, 1, on, P, out_dtype, epilogue, 1, 0, 0, 0)))
+            return rc;
+    }
+    return B200_OK;
+}
+
 } // extern "C"
