@@ -159,6 +159,12 @@ typedef struct {
 int b200_attention_f16(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
                        const b200_strided4* q, const b200_strided4* k, const b200_strided4* v,
                        void* out, int out_dtype, float scale);
+/* Same, with out as an (E,Lq,H,B) view of arbitrary L/H/B strides (E contiguous).  Writing the
+ * token-major layout the next addmm reads — strides {1, E*H, E, E*H*Lq} — folds the
+ * clone/contiguous that follows sdpa in the exported graphs (execute.jl:257-277) into the store. */
+int b200_attention_f16_strided(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
+                               const b200_strided4* q, const b200_strided4* k, const b200_strided4* v,
+                               const b200_strided4* out, int out_dtype, float scale);
 /* flashcm_plan (flash.jl:1322-1374): B200_OK or the Decline reason. */
 int b200_attention_f16_supported(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
                                  const int64_t* qstride, const int64_t* kstride,
@@ -173,6 +179,17 @@ int b200_attention_f16_supported(int64_t E, int64_t Lq, int64_t Lk, int64_t H, i
 int b200_layernorm(b200_ctx* ctx, int64_t groups, int64_t C, const void* a, int in_dtype, void* out,
                    int out_dtype, float* mean, float* rstd, const void* gamma, const void* beta,
                    float eps);
+
+/*
+ * add.Tensor (+ clamp.default) + native_layer_norm in one launch, fp16:
+ *     x <- clamp(fp16(x + h), lo, hi)   (clamp only if use_clamp);   out <- LN(x)
+ * The reference runs these as separate graph ops (ops.jl:186-197,323-335,575-647; its own
+ * fusion of element-wise chains is fuse.jl).  Results are bit-identical to the three ops in
+ * sequence; x is updated in place, x/h/out are (C, groups) contiguous.
+ */
+int b200_add_layernorm_f16(b200_ctx* ctx, int64_t groups, int64_t C, void* x, const void* h, int use_clamp,
+                           float lo, float hi, void* out, float* mean, float* rstd, const void* gamma,
+                           const void* beta, float eps);
 
 /* ------------------------------------------------------- convolution as a GEMM */
 /*

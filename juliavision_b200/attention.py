@@ -58,11 +58,13 @@ def sdpa_(ctx: Ctx, plan, out: Optional[DeviceArray], q, k, v, bias, scale: floa
     if out is None:
         # sdpaout: accum(eltype(q)) = fp32 when the caller gives no destination (attention.jl:761-765)
         out = ctx.allocate(np.float32, E, Lq, H, B)
-    if not out.isdense() or out.shape != (E, Lq, H, B):
-        raise B200Error(17, "sdpa!: out must be dense (E, Lq, H, B)")
-    qs, ks, vs = _s4(q), _s4(k), _s4(v)
-    check(_lib.lib().b200_attention_f16(ctx.handle, E, Lq, Lk, H, B, C.byref(qs), C.byref(ks), C.byref(vs), out.ptr,
-                                        dtcode(out.dtype), float(scale)))
+    if out.shape != (E, Lq, H, B) or (E != 1 and out.strides[0] != 1):
+        raise B200Error(17, "sdpa!: out must be an (E, Lq, H, B) array with E contiguous")
+    # A dense out is the reference's contract; a strided view (e.g. token-major) folds the
+    # permute copy that follows sdpa in the exported graphs into the store.
+    qs, ks, vs, os_ = _s4(q), _s4(k), _s4(v), _s4(out)
+    check(_lib.lib().b200_attention_f16_strided(ctx.handle, E, Lq, Lk, H, B, C.byref(qs), C.byref(ks), C.byref(vs),
+                                                C.byref(os_), dtcode(out.dtype), float(scale)))
     return out
 
 

@@ -43,6 +43,7 @@ struct AttnParams {
     int E, Lq, Lk, H, B;
     float scale_log2;   // scale * log2(e)
     void* out;
+    int64_t osL, osH, osB;  // element strides of out along L, H, B (E is contiguous)
     int out_f32;
     int* d_status;
 };
@@ -293,7 +294,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
             tc_fence_after();
             const float inv = 1.0f / (l_run == 0.f ? 1.0f : l_run);
             const int lq = q0 + row;
-            const int64_t obase = (int64_t)p.E * (lq + (int64_t)p.Lq * (h + (int64_t)p.H * b));
+            const int64_t obase = lq * p.osL + h * p.osH + b * p.osB;
 #pragma unroll 1
             for (int c = 0; c < ATT_EP / 32; ++c) {
                 uint32_t r[32];
@@ -350,7 +351,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
 __global__ void attention_f16_scalar_kernel(int E, int Lq, int Lk, int H, int B, const __half* q, int64_t qsE, int64_t qsL, int64_t qsH, int64_t qsB,
                                             const __half* k, int64_t ksE, int64_t ksL, int64_t ksH, int64_t ksB,
                                             const __half* v, int64_t vsE, int64_t vsL, int64_t vsH, int64_t vsB,
-                                            void* out, int out_f32, float scale) {
+                                            void* out, int64_t osL, int64_t osH, int64_t osB, int out_f32, float scale) {
     const int lane = threadIdx.x & 31;
     const int64_t rowid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (rowid >= (int64_t)Lq * H * B) return;
@@ -390,7 +391,7 @@ __global__ void attention_f16_scalar_kernel(int E, int Lq, int Lk, int H, int B,
     }
     for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
     const float inv = 1.0f / (l == 0.f ? 1.0f : l);
-    const int64_t obase = (int64_t)E * (lq + (int64_t)Lq * (h + (int64_t)H * b));
+    const int64_t obase = lq * osL + h * osH + b * osB;
     for (int e = lane; e < E; e += 32) {
         if (out_f32) static_cast<float*>(out)[obase + e] = acc[e] * inv;
         else static_cast<__half*>(out)[obase + e] = __float2half_rn(acc[e] * inv);
@@ -448,7 +449,20 @@ int b200_attention_f16_supported(int64_t E, int64_t Lq, int64_t Lk, int64_t H, i
 int b200_attention_f16(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
                        const b200_strided4* q, const b200_strided4* k, const b200_strided4* v, void* out,
                        int out_dtype, float scale) {
-    B200_REQUIRE(ctx && q && k && v, B200_EINVAL, "attention: null argument");
+    b200_strided4 o;
+    o.ptr = out;
+    o.stride[0] = 1;
+    o.stride[1] = E;
+    o.stride[2] = E * Lq;
+    o.stride[3] = E * Lq * H;
+    return b200_attention_f16_strided(ctx, E, Lq, Lk, H, B, q, k, v, &o, out_dtype, scale);
+}
+
+int b200_attention_f16_strided(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
+                               const b200_strided4* q, const b200_strided4* k, const b200_strided4* v,
+                               const b200_strided4* o, int out_dtype, float scale) {
+    B200_REQUIRE(ctx && q && k && v && o, B200_EINVAL, "attention: null argument");
+    void* out = const_cast<void*>(o->ptr);
     B200_REQUIRE(E >= 0 && Lq >= 0 && Lk >= 0 && H >= 0 && B >= 0, B200_EINVAL, "attention: negative extent");
     B200_REQUIRE(out_dtype == B200_F16 || out_dtype == B200_F32, B200_DECLINE_ELTYPE, "attention: out dtype %d",
                  out_dtype);
@@ -456,15 +470,21 @@ int b200_attention_f16(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t
     B200_REQUIRE(out && q->ptr, B200_EINVAL, "attention: null array");
     B200_CUDA(cudaSetDevice(ctx->device));
     const size_t osz = out_dtype == B200_F16 ? 2 : 4;
+    const int64_t oal = out_dtype == B200_F16 ? 8 : 4; // elements per 16-byte vector store
+    B200_REQUIRE(o->stride[0] == 1, B200_DECLINE_ALIGN, "attention: out must be contiguous along E");
+    const bool odense = o->stride[1] == E && (H == 1 || o->stride[2] == E * Lq) && (B == 1 || o->stride[3] == E * Lq * H);
+    const bool oaligned = (Lq == 1 || o->stride[1] % oal == 0) && (H == 1 || o->stride[2] % oal == 0) &&
+                          (B == 1 || o->stride[3] % oal == 0);
     if (Lk == 0) {
         // Softmax over no keys: every row is the all-blocked case, a zero row divided by one.
+        B200_REQUIRE(odense, B200_DECLINE_ALIGN, "attention: Lk = 0 with a strided out");
         B200_CUDA(cudaMemsetAsync(out, 0, (size_t)(E * Lq * H * B) * osz, ctx->stream));
         return B200_OK;
     }
     B200_REQUIRE(k->ptr && v->ptr, B200_EINVAL, "attention: null array");
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     const bool tc = tc_reason(E, Lq, Lk, H, B, q->stride, k->stride, v->stride) == B200_OK && al16(q->ptr) &&
-                    al16(k->ptr) && al16(v->ptr) && al16(out);
+                    al16(k->ptr) && al16(v->ptr) && al16(out) && oaligned;
     if (!tc) {
         B200_REQUIRE(E <= 1024, B200_DECLINE_EXTENT, "attention: E = %lld", (long long)E);
         const int wpb = 4;
@@ -473,7 +493,7 @@ int b200_attention_f16(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t
             (int)E, (int)Lq, (int)Lk, (int)H, (int)B, (const __half*)q->ptr, q->stride[0], q->stride[1],
             q->stride[2], q->stride[3], (const __half*)k->ptr, k->stride[0], k->stride[1], k->stride[2],
             k->stride[3], (const __half*)v->ptr, v->stride[0], v->stride[1], v->stride[2], v->stride[3], out,
-            out_dtype == B200_F32, scale);
+            o->stride[1], o->stride[2], o->stride[3], out_dtype == B200_F32, scale);
         ctx->launches++;
         B200_CUDA(cudaGetLastError());
         return B200_OK;
@@ -493,6 +513,7 @@ int b200_attention_f16(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t
     p.E = (int)E; p.Lq = (int)Lq; p.Lk = (int)Lk; p.H = (int)H; p.B = (int)B;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.out = out;
+    p.osL = o->stride[1]; p.osH = o->stride[2]; p.osB = o->stride[3];
     p.out_f32 = out_dtype == B200_F32;
     p.d_status = ctx->d_status;
     dim3 grid((unsigned)cdiv(Lq, ATT_BR), (unsigned)H, (unsigned)B);

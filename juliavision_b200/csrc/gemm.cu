@@ -16,41 +16,50 @@
 //   warp 0    TMA producer  (one lane)        global -> shared ring, STAGES deep
 //   warp 1    UMMA issuer   (one lane)        shared -> TMEM accumulators (two, ping-pong)
 //   warps 2-5 epilogue      (128 threads)     TMEM -> registers -> +bias, round, act ->
-//                                             swizzled shared staging -> TMA store
+//                                             16-byte stores straight to global memory
 #include <cuda_fp16.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 #include "internal.h"
 #include "ptx.cuh"
 
 namespace b200 {
 
-constexpr int GEMM_BM = 128; // tokens per tile (TMEM lanes)
+constexpr int GEMM_BM = 128; // tokens per CTA (TMEM lanes)
 constexpr int GEMM_BK = 64;  // one 128-byte swizzle row of fp16
 constexpr int GEMM_THREADS = 192;
 constexpr int SMEM_LIMIT = 232448; // 227 KB
 
-template <int BN, typename OutT> struct GemmCfg {
+// NCTA = 1: one CTA per tile of 128 tokens x BN features (tcgen05.mma.cta_group::1).
+// NCTA = 2: a cluster of two CTAs per tile of 256 tokens x BN features (cta_group::2, UMMA M = 256):
+//           each CTA stages its own 128 token rows and BN/2 of the feature columns, so the shared
+//           memory traffic per flop halves and the tensor core is no longer starved by it.
+template <int BN, typename OutT, int NCTA> struct GemmCfg {
     static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
     static constexpr int B_CHUNK_BYTES = 64 * GEMM_BK * 2; // one 64-feature slab of the B tile
-    static constexpr int B_BYTES = BN * GEMM_BK * 2;
+    static constexpr int B_COLS = BN / NCTA;               // feature columns this CTA stages
+    static constexpr int B_BYTES = B_COLS * GEMM_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int OUT_COLS = 128 / (int)sizeof(OutT); // columns per 128-byte staging row
-    static constexpr int STG_BYTES = GEMM_BM * 128;
-    static constexpr int TAIL_BYTES = 2 * STG_BYTES + BN * 4 + 256;
-    static constexpr int STAGES_RAW = (SMEM_LIMIT - 1024 - TAIL_BYTES) / STAGE_BYTES;
+    static constexpr int TAIL_BYTES = 4 * BN * 2 + 256; // per-warp fp16 bias + barriers
+    static constexpr int STAGES_RAW = (SMEM_LIMIT - TAIL_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + TAIL_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TAIL_BYTES;
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
     static_assert(STAGES >= 2, "ring too shallow");
     static_assert(SMEM_BYTES <= SMEM_LIMIT, "shared memory over budget");
     static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
+    static_assert(B_COLS % 64 == 0, "each CTA stages whole 64-column slabs of B");
 };
 
-struct GemmParams {
+template <typename OutT> struct GemmParams {
     int64_t M, N, K;       // out features, tokens, reduction
     int tiles_m, tiles_n;  // feature tiles, token tiles
     int64_t total_tiles;   // tiles_m * tiles_n * nbatch
     int num_kb;
+    OutT* out;             // out(M,N): element (i,j) of plane b at out[b*strideO + j*ldo + i]
+    int64_t ldo, strideO;
     const __half* bias;
     int bias_per_n;        // 0: bias[i] over features (M); 1: bias[j] over tokens (N)
     int epilogue;
@@ -77,28 +86,36 @@ __device__ __forceinline__ float apply_act(int epi, float v) {
     }
 }
 
-template <int BN, typename OutT>
+template <int BN, typename OutT, int NCTA>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, tokens, batch}
                    const __grid_constant__ CUtensorMap tmapW,   // A(M,K): {features, K, batch}
-                   const __grid_constant__ CUtensorMap tmapO,   // out(M,N): {features, tokens, batch}
-                   const GemmParams p) {
-    using Cfg = GemmCfg<BN, OutT>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                               ~uintptr_t(1023));
-    uint8_t* stg = smem + Cfg::STAGES * Cfg::STAGE_BYTES;
-    float* sbias = reinterpret_cast<float*>(stg + 2 * Cfg::STG_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sbias) + BN * 4);
-    uint64_t* full = bars;                     // [STAGES]
+                   const GemmParams<OutT> p) {
+    using Cfg = GemmCfg<BN, OutT, NCTA>;
+    constexpr int TILE_N = GEMM_BM * NCTA; // tokens per tile
+    // The swizzled tiles need a 1024-byte aligned base.  The declaration asks for it; should a
+    // toolchain not honour that, every thread of the grid sees the same misaligned offset and
+    // leaves before any barrier, cluster sync or TMEM allocation exists.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    if ((smem_u32(smem_raw) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicCAS(p.d_status, 0, KST_SMEM_LAYOUT);
+        return;
+    }
+    __half* sbias = reinterpret_cast<__half*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sbias) + 4 * BN * 2);
+    uint64_t* full = bars;                     // [STAGES]  (pair: only the leader's are used)
     uint64_t* empty = bars + Cfg::STAGES;      // [STAGES]
     uint64_t* tfull = bars + 2 * Cfg::STAGES;  // [2]
-    uint64_t* tempty = tfull + 2;              // [2]
+    uint64_t* tempty = tfull + 2;              // [2]      (pair: only the leader's are used)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t rank = NCTA == 2 ? cluster_ctarank() : 0u;  // 0 = the CTA that issues the UMMAs
+    const int64_t worker = NCTA == 2 ? (blockIdx.x >> 1) : blockIdx.x;
+    const int64_t nworkers = NCTA == 2 ? (gridDim.x >> 1) : gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) {
@@ -107,20 +124,25 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tfull[a], 1);
-            mbar_init(&tempty[a], 4);
+            mbar_init(&tempty[a], 4 * NCTA);
         }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tmapX);
         prefetch_tmap(&tmapW);
-        prefetch_tmap(&tmapO);
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-        tmem_relinquish();
+        if constexpr (NCTA == 2) {
+            tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if constexpr (NCTA == 2) cluster_sync_all(); // both CTAs' barriers and TMEM exist before any use
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -132,11 +154,11 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+            for (int64_t tile = worker; ok && tile < p.total_tiles; tile += nworkers) {
                 const int batch = (int)(tile / tiles_per_batch);
                 const int rem = (int)(tile % tiles_per_batch);
-                const int m0 = (rem % p.tiles_m) * BN;
-                const int n0 = (rem / p.tiles_m) * GEMM_BM;
+                const int m0 = (rem % p.tiles_m) * BN + (int)rank * Cfg::B_COLS;
+                const int n0 = (rem / p.tiles_m) * TILE_N + (int)rank * GEMM_BM;
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     if (!mbar_wait(&empty[s], ph ^ 1, p.d_status, KST_WAIT_EMPTY, abort_flag)) {
                         ok = false;
@@ -144,34 +166,51 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                     }
                     uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
                     uint8_t* sb = sa + Cfg::A_BYTES;
-                    mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
-                    tma_load_3d(sa, &tmapX, &full[s], kb * GEMM_BK, n0, batch);
+                    if constexpr (NCTA == 2) {
+                        // Both CTAs' bytes are counted on the leader's barrier; the leader posts
+                        // the expectation for the pair.
+                        const uint32_t bar = mapa_u32(smem_u32(&full[s]), 0);
+                        if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * Cfg::STAGE_BYTES);
+                        tma_load_3d_pair(sa, &tmapX, bar, kb * GEMM_BK, n0, batch);
 #pragma unroll
-                    for (int j = 0; j < BN / 64; ++j)
-                        tma_load_3d(sb + j * Cfg::B_CHUNK_BYTES, &tmapW, &full[s], m0 + j * 64,
-                                    kb * GEMM_BK, batch);
+                        for (int j = 0; j < Cfg::B_COLS / 64; ++j)
+                            tma_load_3d_pair(sb + j * Cfg::B_CHUNK_BYTES, &tmapW, bar, m0 + j * 64, kb * GEMM_BK, batch);
+                    } else {
+                        mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
+                        tma_load_3d(sa, &tmapX, &full[s], kb * GEMM_BK, n0, batch);
+#pragma unroll
+                        for (int j = 0; j < Cfg::B_COLS / 64; ++j)
+                            tma_load_3d(sb + j * Cfg::B_CHUNK_BYTES, &tmapW, &full[s], m0 + j * 64, kb * GEMM_BK, batch);
+                    }
                     if (++s == Cfg::STAGES) { s = 0; ph ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         // -------------------------------------------------------------- UMMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_f16(GEMM_BM, BN, /*a K-major*/ 0, /*b MN-major*/ 1);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_f16(TILE_N, BN, /*a K-major*/ 0, /*b MN-major*/ 1);
             constexpr uint64_t adesc0 = make_smem_desc(16, 1024);
             constexpr uint64_t bdesc0 = make_smem_desc(Cfg::B_CHUNK_BYTES, 1024);
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
             int64_t it = 0;
-            for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++it) {
+            for (int64_t tile = worker; ok && tile < p.total_tiles; tile += nworkers, ++it) {
                 const int acc = (int)(it & 1);
                 const uint32_t aph = (uint32_t)((it >> 1) & 1);
-                if (!mbar_wait(&tempty[acc], aph ^ 1, p.d_status, KST_WAIT_TMEM_EMPTY, abort_flag)) break;
+                if constexpr (NCTA == 2) {
+                    if (!mbar_wait_cluster(&tempty[acc], aph ^ 1, p.d_status, KST_WAIT_TMEM_EMPTY, abort_flag)) break;
+                } else {
+                    if (!mbar_wait(&tempty[acc], aph ^ 1, p.d_status, KST_WAIT_TMEM_EMPTY, abort_flag)) break;
+                }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!mbar_wait(&full[s], ph, p.d_status, KST_WAIT_FULL, abort_flag)) {
+                    bool got;
+                    if constexpr (NCTA == 2) got = mbar_wait_cluster(&full[s], ph, p.d_status, KST_WAIT_FULL, abort_flag);
+                    else got = mbar_wait(&full[s], ph, p.d_status, KST_WAIT_FULL, abort_flag);
+                    if (!got) {
                         ok = false;
                         break;
                     }
@@ -182,39 +221,46 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                     for (int k = 0; k < GEMM_BK / 16; ++k) {
                         // K-major A: +16 elements of K = +32 B inside the swizzle row.
                         // MN-major B: +16 k-rows = two 8-row groups = +2048 B.
-                        umma_ss(d_tmem, smem_desc_at(adesc0, a_addr + k * 32),
-                                smem_desc_at(bdesc0, b_addr + k * 2048), idesc, (kb | k) != 0);
+                        const uint64_t ad = smem_desc_at(adesc0, a_addr + k * 32);
+                        const uint64_t bd = smem_desc_at(bdesc0, b_addr + k * 2048);
+                        if constexpr (NCTA == 2) umma_ss_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
+                        else umma_ss(d_tmem, ad, bd, idesc, (kb | k) != 0);
                     }
-                    umma_commit(&empty[s]);
+                    if constexpr (NCTA == 2) umma_commit_pair(&empty[s], 3); // frees the stage in both CTAs
+                    else umma_commit(&empty[s]);
                     if (++s == Cfg::STAGES) { s = 0; ph ^= 1; }
                 }
-                if (ok) umma_commit(&tfull[acc]);
+                if (ok) {
+                    if constexpr (NCTA == 2) umma_commit_pair(&tfull[acc], 3);
+                    else umma_commit(&tfull[acc]);
+                }
             }
         }
     } else {
         // ---------------------------------------------------------------- epilogue
-        const int et = threadIdx.x - 64;       // 0..127
+        // Each warp owns the 32 token rows of its TMEM lane quadrant end to end: its own bias copy,
+        // its own two staging slabs (32 rows x 128 B) and its own TMA stores, so the four warps
+        // never wait for one another.
+        const int ew = warp - 2;               // 0..3
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
-        const int row = quad * 32 + lane;      // token row inside the tile
-        uint32_t chunk_ctr = 0;
+        const int row = quad * 32 + lane;      // token row inside this CTA's half of the tile
+        __half* wbias = sbias + ew * BN;
         int64_t it = 0;
-        for (int64_t tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
+        for (int64_t tile = worker; tile < p.total_tiles; tile += nworkers, ++it) {
             const int batch = (int)(tile / tiles_per_batch);
             const int rem = (int)(tile % tiles_per_batch);
             const int m0 = (rem % p.tiles_m) * BN;
-            const int n0 = (rem / p.tiles_m) * GEMM_BM;
+            const int n0 = (rem / p.tiles_m) * TILE_N + (int)rank * GEMM_BM;
             const int acc = (int)(it & 1);
             const uint32_t aph = (uint32_t)((it >> 1) & 1);
 
-            named_bar_sync(1, 128); // previous tile's bias readers are done
-            for (int j = et; j < BN; j += 128)
-                sbias[j] = (p.bias != nullptr && !p.bias_per_n && m0 + j < p.M) ? __half2float(p.bias[m0 + j]) : 0.f;
+            __syncwarp(); // the previous tile's readers of wbias are done
+            for (int j = lane; j < BN; j += 32)
+                wbias[j] = (p.bias != nullptr && !p.bias_per_n && m0 + j < p.M) ? p.bias[m0 + j] : __float2half(0.f);
             const float rbias =
                 (p.bias != nullptr && p.bias_per_n && n0 + row < p.N) ? __half2float(p.bias[n0 + row]) : 0.f;
             const bool got = mbar_wait(&tfull[acc], aph, p.d_status, KST_WAIT_TMEM_FULL, abort_flag);
-            // One answer for all 128 threads: a split decision would strand the rest at the
-            // barriers inside the chunk loop.
-            if (named_bar_or(1, 128, !got || *abort_flag != 0)) break;
+            if (__any_sync(0xffffffffu, !got)) break; // one answer per warp
             tc_fence_after();
 
             constexpr int NCHUNK = BN / Cfg::OUT_COLS;
@@ -224,32 +270,38 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                 float v[Cfg::OUT_COLS];
                 {
                     const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN + col0;
-                    uint32_t r[32];
-                    tmem_ld32(taddr, r);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) + rbias;
+                    uint32_t r0[32];
+                    tmem_ld32(taddr, r0);
                     if constexpr (Cfg::OUT_COLS == 64) {
-                        tmem_ld32(taddr + 32, r);
+                        uint32_t r1[32];
+                        tmem_ld32(taddr + 32, r1);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[32 + i] = __uint_as_float(r[i]) + rbias;
+                        for (int i = 0; i < 32; ++i) v[32 + i] = __uint_as_float(r1[i]) + rbias;
+                    } else {
+                        tmem_wait_ld();
                     }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r0[i]) + rbias;
                 }
                 if (c == NCHUNK - 1) {
-                    // Accumulator fully read: hand it back to the UMMA issuer.
+                    // Accumulator fully read: hand it back to the UMMA issuer (in the leader CTA).
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&tempty[acc]);
+                    if (lane == 0) {
+                        if constexpr (NCTA == 2) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
+                        else mbar_arrive(&tempty[acc]);
+                    }
                 }
-                if (m0 + col0 >= p.M) continue; // whole chunk past the feature extent
+                const int tok = n0 + row;
+                if (m0 + col0 >= p.M || tok >= p.N) continue; // nothing of this row chunk is inside the output
 
-                uint8_t* buf = stg + (chunk_ctr & 1) * Cfg::STG_BYTES;
-                ++chunk_ctr;
-                if (et == 0) tma_store_wait_read<1>(); // the store that last read `buf` is done
-                named_bar_sync(1, 128);
-
-                uint8_t* rowp = buf + row * 128;
+                // Straight from registers to global memory: each thread owns OUT_COLS consecutive
+                // features of one token, i.e. 128 contiguous bytes, written as 16-byte vectors.  No
+                // staging and no completion to wait for, which is what a tile with a short K loop
+                // (where nothing hides the epilogue) needs.
+                OutT* gout = p.out + (size_t)batch * p.strideO + (size_t)tok * p.ldo + (m0 + col0);
+                const int valid = (int)(p.M - (m0 + col0)) < Cfg::OUT_COLS ? (int)(p.M - (m0 + col0)) : Cfg::OUT_COLS;
                 if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -259,36 +311,41 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         for (int q = 0; q < 4; ++q) {
                             const int cidx = j * 8 + q * 2;
                             // Round to fp16 first; the activation sees the rounded value.
-                            __half2 t = __floats2half2_rn(v[cidx] + sbias[col0 + cidx],
-                                                          v[cidx + 1] + sbias[col0 + cidx + 1]);
+                            const float2 bb = __half22float2(*reinterpret_cast<const __half2*>(&wbias[col0 + cidx]));
+                            __half2 t = __floats2half2_rn(v[cidx] + bb.x, v[cidx + 1] + bb.y);
                             if (p.epilogue != B200_EPI_NONE) {
                                 float2 f = __half22float2(t);
                                 t = __floats2half2_rn(apply_act(p.epilogue, f.x), apply_act(p.epilogue, f.y));
                             }
                             h[q] = t;
                         }
-                        *reinterpret_cast<uint4*>(rowp + ((j ^ (row & 7)) << 4)) = o;
+                        if (j * 8 + 8 <= valid) {
+                            *reinterpret_cast<uint4*>(gout + j * 8) = o;
+                        } else {
+                            const __half* e = reinterpret_cast<const __half*>(&o);
+                            for (int t = 0; t < 8; ++t)
+                                if (j * 8 + t < valid) gout[j * 8 + t] = e[t];
+                        }
                     }
                 } else {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         float4 o;
-                        o.x = apply_act(p.epilogue, v[j * 4 + 0] + sbias[col0 + j * 4 + 0]);
-                        o.y = apply_act(p.epilogue, v[j * 4 + 1] + sbias[col0 + j * 4 + 1]);
-                        o.z = apply_act(p.epilogue, v[j * 4 + 2] + sbias[col0 + j * 4 + 2]);
-                        o.w = apply_act(p.epilogue, v[j * 4 + 3] + sbias[col0 + j * 4 + 3]);
-                        *reinterpret_cast<float4*>(rowp + ((j ^ (row & 7)) << 4)) = o;
+                        o.x = apply_act(p.epilogue, v[j * 4 + 0] + __half2float(wbias[col0 + j * 4 + 0]));
+                        o.y = apply_act(p.epilogue, v[j * 4 + 1] + __half2float(wbias[col0 + j * 4 + 1]));
+                        o.z = apply_act(p.epilogue, v[j * 4 + 2] + __half2float(wbias[col0 + j * 4 + 2]));
+                        o.w = apply_act(p.epilogue, v[j * 4 + 3] + __half2float(wbias[col0 + j * 4 + 3]));
+                        if (j * 4 + 4 <= valid) {
+                            *reinterpret_cast<float4*>(gout + j * 4) = o;
+                        } else {
+                            const float* e = reinterpret_cast<const float*>(&o);
+                            for (int t = 0; t < 4; ++t)
+                                if (j * 4 + t < valid) gout[j * 4 + t] = e[t];
+                        }
                     }
-                }
-                fence_proxy_async_smem();
-                named_bar_sync(1, 128);
-                if (et == 0) {
-                    tma_store_3d(&tmapO, buf, m0 + col0, n0, batch);
-                    tma_store_commit();
                 }
             }
         }
-        if (et == 0) tma_store_wait_all<0>();
     }
 
     // Teardown: every role arrives here whether it finished or gave up.
@@ -297,10 +354,12 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         for (int i = 0; i < 4; ++i) __nanosleep(1000000);
     }
     tc_fence_before();
-    __syncthreads();
+    if constexpr (NCTA == 2) cluster_sync_all(); // neither CTA leaves while its peer may still signal it
+    else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+        if constexpr (NCTA == 2) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+        else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
 }
 
@@ -329,39 +388,52 @@ __global__ void gemm_f16_scalar_kernel(int64_t M, int64_t N, int64_t K, const __
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Tile planner: feature-tile width BN in {256,128,64} minimising (waves x tile cost), the
-// cost of a tile taken as proportional to BN plus a fixed per-tile overhead.
-static int pick_bn(int64_t M, int64_t N, int64_t nbatch, int sms) {
-    int best = 256;
+struct TilePick {
+    int bn;    // feature columns per tile
+    int ncta;  // 1: 128-token tiles, one CTA each; 2: 256-token tiles, one CTA pair each
+};
+
+// Tile planner.  Candidates are (BN, NCTA); the cost of a launch is waves x (per-tile main loop +
+// a fixed per-tile cost), in units of "one CTA pair at full tensor rate".  Single-CTA tiles feed
+// the tensor core from shared memory below its rate (measured ~0.73 at BN=256, less for narrower
+// tiles); pair tiles run it at rate but need twice the tokens to fill a tile.
+static TilePick pick_tile(int64_t M, int64_t N, int64_t nbatch, int sms) {
+    if (const char* f = getenv("B200_GEMM_TILE")) { // debugging aid: "<bn>x<ncta>", e.g. 256x2
+        int bn = 0, nc = 0;
+        if (sscanf(f, "%dx%d", &bn, &nc) == 2 && (bn == 256 || bn == 128 || (bn == 64 && nc == 1)) && (nc == 1 || nc == 2))
+            return {bn, nc};
+    }
+    struct Cand { int bn, ncta; double rate; };
+    const Cand cands[5] = {{256, 2, 1.0}, {128, 2, 0.70}, {256, 1, 0.73}, {128, 1, 0.62}, {64, 1, 0.42}};
+    TilePick best{256, 1};
     double best_cost = 1e300;
-    const int cands[3] = {256, 128, 64};
-    for (int bn : cands) {
-        int64_t tiles = cdiv(M, bn) * cdiv(N, GEMM_BM) * nbatch;
-        int64_t waves = cdiv(tiles, sms);
-        // Narrow tiles re-read the activation tile more often and run the tensor core below
-        // its shared-memory feed rate: weight them accordingly.
-        double eff = bn == 256 ? 1.0 : (bn == 128 ? 1.1 : 1.5);
-        double cost = (double)waves * (bn * eff + 24.0);
-        if (cost < best_cost) {
+    for (const Cand& c : cands) {
+        const int64_t tiles = cdiv(M, c.bn) * cdiv(N, (int64_t)GEMM_BM * c.ncta) * nbatch;
+        const int64_t workers = sms / c.ncta;
+        const int64_t waves = cdiv(tiles, workers);
+        // work per tile relative to a 256x256 pair tile, divided by the rate it runs at
+        const double tile_work = (double)c.bn * c.ncta / 512.0 / c.rate * (c.ncta == 2 ? 1.0 : 2.0);
+        const double cost = (double)waves * (tile_work + 0.08);
+        if (cost < best_cost - 1e-9) {
             best_cost = cost;
-            best = bn;
+            best = {c.bn, c.ncta};
         }
     }
     return best;
 }
 
-template <int BN, typename OutT>
+template <int BN, typename OutT, int NCTA>
 static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
                      const void* B, int64_t ldb, const void* bias, int bias_per_n, void* out, int64_t ldo,
                      int epi, int64_t nbatch, int64_t sA, int64_t sB, int64_t sO) {
-    using Cfg = GemmCfg<BN, OutT>;
+    using Cfg = GemmCfg<BN, OutT, NCTA>;
     static bool attr_done[16] = {};
-    auto kern = gemm_f16_tc_kernel<BN, OutT>;
+    auto kern = gemm_f16_tc_kernel<BN, OutT, NCTA>;
     if (!attr_done[ctx->device & 15]) {
         B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_done[ctx->device & 15] = true;
     }
-    CUtensorMap tX, tW, tO;
+    CUtensorMap tX, tW;
     {
         uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)nbatch};
         uint64_t str[2] = {(uint64_t)ldb * 2, (uint64_t)(nbatch > 1 ? sB : ldb * N) * 2};
@@ -378,30 +450,51 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
                            CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
     }
-    {
-        uint64_t dims[3] = {(uint64_t)M, (uint64_t)N, (uint64_t)nbatch};
-        uint64_t str[2] = {(uint64_t)ldo * sizeof(OutT), (uint64_t)(nbatch > 1 ? sO : ldo * N) * sizeof(OutT)};
-        uint32_t box[3] = {(uint32_t)Cfg::OUT_COLS, GEMM_BM, 1};
-        int rc = make_tmap(ctx, &tO, sizeof(OutT) == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
-                           3, out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (rc) return rc;
-    }
-    GemmParams p;
+    GemmParams<OutT> p;
     p.M = M; p.N = N; p.K = K;
+    p.out = static_cast<OutT*>(out);
+    p.ldo = ldo;
+    p.strideO = nbatch > 1 ? sO : 0;
     p.tiles_m = (int)cdiv(M, BN);
-    p.tiles_n = (int)cdiv(N, GEMM_BM);
+    p.tiles_n = (int)cdiv(N, (int64_t)GEMM_BM * NCTA);
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * nbatch;
     p.num_kb = (int)cdiv(K, GEMM_BK);
     p.bias = static_cast<const __half*>(bias);
     p.bias_per_n = bias_per_n;
     p.epilogue = epi;
     p.d_status = ctx->d_status;
-    int grid = (int)(p.total_tiles < ctx->prop.multiProcessorCount ? p.total_tiles
-                                                                   : ctx->prop.multiProcessorCount);
-    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(tX, tW, tO, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = NCTA;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // Persistent workers: as many CTAs (or CTA pairs) as can be resident at once.  Pairs must sit
+    // in one GPC, so fewer than SMs/2 may fit; ask the runtime once per device.
+    static int resident[16] = {};
+    int64_t workers_max = ctx->prop.multiProcessorCount / NCTA;
+    if (NCTA == 2) {
+        if (!resident[ctx->device & 15]) {
+            int n = 0;
+            cfg.gridDim = dim3((unsigned)(workers_max * NCTA), 1, 1);
+            cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+            if (e != cudaSuccess || n <= 0) {
+                cudaGetLastError();
+                n = (int)workers_max;
+            }
+            resident[ctx->device & 15] = n;
+        }
+        if (resident[ctx->device & 15] < workers_max) workers_max = resident[ctx->device & 15];
+    }
+    const int workers = (int)(p.total_tiles < workers_max ? p.total_tiles : workers_max);
+    cfg.gridDim = dim3((unsigned)(workers * NCTA), 1, 1);
+    B200_CUDA(cudaLaunchKernelEx(&cfg, kern, tX, tW, p));
     ctx->launches++;
-    B200_CUDA(cudaGetLastError());
     return B200_OK;
 }
 
@@ -432,18 +525,26 @@ int b200_gemm_f16_plan(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t n
     B200_REQUIRE(ctx && plan, B200_EINVAL, "gemm_plan: null argument");
     B200_REQUIRE(M >= 1 && N >= 1 && K >= 1 && nbatch >= 1, B200_DECLINE_EXTENT, "gemm_plan: empty extent");
     const int sms = ctx->prop.multiProcessorCount;
-    int bn = pick_bn(M, N, nbatch, sms);
-    plan->block_m = GEMM_BM;
+    const TilePick t = pick_tile(M, N, nbatch, sms);
+    const int bn = t.bn;
+    plan->block_m = GEMM_BM * t.ncta;
     plan->block_n = bn;
     plan->block_k = GEMM_BK;
-    plan->stages = bn == 256 ? GemmCfg<256, __half>::STAGES
-                             : (bn == 128 ? GemmCfg<128, __half>::STAGES : GemmCfg<64, __half>::STAGES);
-    plan->smem_bytes = bn == 256 ? GemmCfg<256, __half>::SMEM_BYTES
-                                 : (bn == 128 ? GemmCfg<128, __half>::SMEM_BYTES : GemmCfg<64, __half>::SMEM_BYTES);
+    if (t.ncta == 2) {
+        plan->stages = bn == 256 ? GemmCfg<256, __half, 2>::STAGES : GemmCfg<128, __half, 2>::STAGES;
+        plan->smem_bytes = bn == 256 ? GemmCfg<256, __half, 2>::SMEM_BYTES : GemmCfg<128, __half, 2>::SMEM_BYTES;
+    } else {
+        plan->stages = bn == 256 ? GemmCfg<256, __half, 1>::STAGES
+                                 : (bn == 128 ? GemmCfg<128, __half, 1>::STAGES : GemmCfg<64, __half, 1>::STAGES);
+        plan->smem_bytes = bn == 256 ? GemmCfg<256, __half, 1>::SMEM_BYTES
+                                     : (bn == 128 ? GemmCfg<128, __half, 1>::SMEM_BYTES
+                                                  : GemmCfg<64, __half, 1>::SMEM_BYTES);
+    }
     plan->tiles_m = (int)cdiv(M, bn);
-    plan->tiles_n = (int)cdiv(N, GEMM_BM);
-    int64_t tiles = (int64_t)plan->tiles_m * plan->tiles_n * nbatch;
-    plan->ctas = (int)(tiles < sms ? tiles : sms);
+    plan->tiles_n = (int)cdiv(N, (int64_t)GEMM_BM * t.ncta);
+    const int64_t tiles = (int64_t)plan->tiles_m * plan->tiles_n * nbatch;
+    const int64_t workers = sms / t.ncta;
+    plan->ctas = (int)((tiles < workers ? tiles : workers) * t.ncta);
     return B200_OK;
 }
 
@@ -494,18 +595,22 @@ int gemm_f16_run(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, 
         B200_CUDA(cudaGetLastError());
         return B200_OK;
     }
-    const int bn = pick_bn(M, N, nbatch, ctx->prop.multiProcessorCount);
-#define GEMM_GO(BN_, T_) \
-    return launch_tc<BN_, T_>(ctx, M, N, K, A, lda, B, ldb, bias, bias_per_n, out, ldo, epilogue, nbatch, strideA, \
-                              strideB, strideO)
+    const TilePick t = pick_tile(M, N, nbatch, ctx->prop.multiProcessorCount);
+#define GEMM_GO(BN_, T_, NC_)                                                                                     \
+    return launch_tc<BN_, T_, NC_>(ctx, M, N, K, A, lda, B, ldb, bias, bias_per_n, out, ldo, epilogue, nbatch, strideA, \
+                                   strideB, strideO)
     if (out_dtype == B200_F16) {
-        if (bn == 256) GEMM_GO(256, __half);
-        if (bn == 128) GEMM_GO(128, __half);
-        GEMM_GO(64, __half);
+        if (t.ncta == 2 && t.bn == 256) GEMM_GO(256, __half, 2);
+        if (t.ncta == 2) GEMM_GO(128, __half, 2);
+        if (t.bn == 256) GEMM_GO(256, __half, 1);
+        if (t.bn == 128) GEMM_GO(128, __half, 1);
+        GEMM_GO(64, __half, 1);
     } else {
-        if (bn == 256) GEMM_GO(256, float);
-        if (bn == 128) GEMM_GO(128, float);
-        GEMM_GO(64, float);
+        if (t.ncta == 2 && t.bn == 256) GEMM_GO(256, float, 2);
+        if (t.ncta == 2) GEMM_GO(128, float, 2);
+        if (t.bn == 256) GEMM_GO(256, float, 1);
+        if (t.bn == 128) GEMM_GO(128, float, 1);
+        GEMM_GO(64, float, 1);
     }
 #undef GEMM_GO
 }

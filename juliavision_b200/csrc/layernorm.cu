@@ -137,6 +137,93 @@ ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restr
     }
 }
 
+// Residual add (+ optional clamp) fused in front of the layer norm, fp16 only:
+//     x <- clamp(fp16(x + h), lo, hi);   out <- LN(x)
+// Bit-identical to running add.Tensor, clamp.default and native_layer_norm one after another
+// (each rounds to fp16 where the separate ops would), but x and h are read once and the three
+// launches become one.
+template <int VPL>
+__global__ void __launch_bounds__(128)
+ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half* __restrict__ out,
+                   float* __restrict__ mean, float* __restrict__ rstd, const __half* __restrict__ gamma,
+                   const __half* __restrict__ beta, int64_t groups, int C, float eps, int use_clamp, float lo,
+                   float hi) {
+    constexpr int VN = 8;
+    const int lane = threadIdx.x & 31;
+    const int64_t g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (g >= groups) return;
+    const int nvec = C / VN;
+    __half* xr = x + g * (int64_t)C;
+    const __half* hr = h + g * (int64_t)C;
+
+    float v[VPL][VN];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int vi = lane + 32 * i;
+        if (vi < nvec) {
+            Vec16<__half> a, b;
+            a.raw = *(reinterpret_cast<const uint4*>(xr) + vi);
+            b.raw = __ldg(reinterpret_cast<const uint4*>(hr) + vi);
+            float fa[VN], fb[VN];
+            a.to_f32(fa);
+            b.to_f32(fb);
+#pragma unroll
+            for (int j = 0; j < VN; ++j) {
+                float t = __half2float(__float2half_rn(fa[j] + fb[j]));        // add.Tensor rounds here
+                if (use_clamp) t = __half2float(__float2half_rn(fminf(fmaxf(t, lo), hi)));
+                v[i][j] = t;
+                s += t;
+            }
+            store_vec<VN>(xr + (int64_t)vi * VN, v[i]);                         // exact: already fp16 values
+        }
+    }
+    const float n = (float)C;
+    const float mu = warp_sum(s) / n;
+    float s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+        if (lane + 32 * i < nvec) {
+#pragma unroll
+            for (int j = 0; j < VN; ++j) {
+                float d = v[i][j] - mu;
+                s2 += d * d;
+            }
+        }
+    const float r = 1.0f / sqrtf(warp_sum(s2) / n + eps);
+    __half* dst = out + g * (int64_t)C;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int vi = lane + 32 * i;
+        if (vi < nvec) {
+            float y[VN];
+#pragma unroll
+            for (int j = 0; j < VN; ++j) y[j] = (v[i][j] - mu) * r;
+            if (gamma) {
+                Vec16<__half> t;
+                float gf[VN];
+                t.raw = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
+                t.to_f32(gf);
+#pragma unroll
+                for (int j = 0; j < VN; ++j) y[j] *= gf[j];
+            }
+            if (beta) {
+                Vec16<__half> t;
+                float bf[VN];
+                t.raw = __ldg(reinterpret_cast<const uint4*>(beta) + vi);
+                t.to_f32(bf);
+#pragma unroll
+                for (int j = 0; j < VN; ++j) y[j] += bf[j];
+            }
+            store_vec<VN>(dst + (int64_t)vi * VN, y);
+        }
+    }
+    if (lane == 0) {
+        mean[g] = mu;
+        rstd[g] = r;
+    }
+}
+
 __device__ __forceinline__ float ldf(const __half* p, int64_t i) { return __half2float(p[i]); }
 __device__ __forceinline__ float ldf(const float* p, int64_t i) { return p[i]; }
 __device__ __forceinline__ void stf(__half* p, int64_t i, float v) { p[i] = __float2half_rn(v); }
@@ -208,8 +295,12 @@ static int launch_ln(b200_ctx* ctx, int64_t groups, int64_t C, const void* a, vo
                                                                   (int)C, eps)
         if (vpl <= 1) LN_GO(1);
         else if (vpl <= 2) LN_GO(2);
+        else if (vpl <= 3) LN_GO(3);
         else if (vpl <= 4) LN_GO(4);
+        else if (vpl <= 5) LN_GO(5);
+        else if (vpl <= 6) LN_GO(6);
         else if (vpl <= 8) LN_GO(8);
+        else if (vpl <= 12) LN_GO(12);
         else LN_GO(16);
 #undef LN_GO
     } else {
@@ -224,6 +315,47 @@ static int launch_ln(b200_ctx* ctx, int64_t groups, int64_t C, const void* a, vo
 } // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_add_layernorm_f16(b200_ctx* ctx, int64_t groups, int64_t C, void* x, const void* h, int use_clamp,
+                                      float lo, float hi, void* out, float* mean, float* rstd, const void* gamma,
+                                      const void* beta, float eps) {
+    B200_REQUIRE(ctx, B200_EINVAL, "add_layernorm: null ctx");
+    B200_REQUIRE(groups >= 0 && C > 0, B200_EINVAL, "add_layernorm: groups=%lld C=%lld", (long long)groups,
+                 (long long)C);
+    if (groups == 0) return B200_OK;
+    B200_REQUIRE(x && h && out && mean && rstd, B200_EINVAL, "add_layernorm: null array");
+    B200_REQUIRE(groups < (1ll << 31), B200_DECLINE_EXTENT, "add_layernorm: %lld groups", (long long)groups);
+    B200_CUDA(cudaSetDevice(ctx->device));
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const bool vec = C % 8 == 0 && C / 8 <= 32 * 16 && al16(x) && al16(h) && al16(out) && (!gamma || al16(gamma)) &&
+                     (!beta || al16(beta));
+    if (!vec) {
+        // Shapes the vector kernel does not take: the three ops one after another, same results.
+        int rc = b200_add_f16(ctx, x, h, x, groups * C);
+        if (rc == B200_OK && use_clamp) rc = b200_clamp_f16(ctx, x, x, groups * C, lo, hi);
+        if (rc != B200_OK) return rc;
+        return b200_layernorm(ctx, groups, C, x, B200_F16, out, B200_F16, mean, rstd, gamma, beta, eps);
+    }
+    const int nvec = (int)(C / 8), vpl = (nvec + 31) / 32, wpb = 4;
+    dim3 grid((unsigned)cdiv(groups, wpb)), block(32 * wpb);
+#define LNA_GO(V)                                                                                               \
+    ln_add_warp_kernel<V><<<grid, block, 0, ctx->stream>>>((__half*)x, (const __half*)h, (__half*)out, mean, rstd, \
+                                                            (const __half*)gamma, (const __half*)beta, groups,     \
+                                                            (int)C, eps, use_clamp, lo, hi)
+    if (vpl <= 1) LNA_GO(1);
+    else if (vpl <= 2) LNA_GO(2);
+    else if (vpl <= 3) LNA_GO(3);
+    else if (vpl <= 4) LNA_GO(4);
+    else if (vpl <= 5) LNA_GO(5);
+    else if (vpl <= 6) LNA_GO(6);
+    else if (vpl <= 8) LNA_GO(8);
+    else if (vpl <= 12) LNA_GO(12);
+    else LNA_GO(16);
+#undef LNA_GO
+    ctx->launches++;
+    B200_CUDA(cudaGetLastError());
+    return B200_OK;
+}
 
 extern "C" int b200_layernorm(b200_ctx* ctx, int64_t groups, int64_t C, const void* a, int in_dtype,
                               void* out, int out_dtype, float* mean, float* rstd, const void* gamma,

@@ -21,7 +21,7 @@ import numpy as np
 from .attention import sdpa
 from .context import Ctx, DeviceArray
 from .elementwise import add_, clamp_
-from .layernorm import layernorm_
+from .layernorm import add_layernorm_, layernorm_
 from .matmul import matmul_
 
 F16_MAX = 65504.0
@@ -80,8 +80,13 @@ class Encoder:
     """Device-resident encoder: weights uploaded once (transposed to the dense (out,K)
     column-major form `hoistpermutes` produces), activations in one preallocated slab."""
 
-    def __init__(self, ctx: Ctx, cfg: EncoderConfig, weights: Optional[List[dict]] = None):
-        self.ctx, self.cfg = ctx, cfg
+    def __init__(self, ctx: Ctx, cfg: EncoderConfig, weights: Optional[List[dict]] = None, fused: bool = True):
+        """`fused=False` issues the exported graph's ops one by one.  `fused=True` applies three
+        load-time rewrites of the kind the reference's `Model` constructor runs (hoistpermutes,
+        foldrelu, fuse): the q/k/v projections share one GEMM over concatenated weights, sdpa
+        writes token-major so the clone after it disappears, and each residual add (+ clamp) is
+        folded into the layer norm that follows.  Same values either way."""
+        self.ctx, self.cfg, self.fused = ctx, cfg, fused
         weights = weights if weights is not None else init_weights(cfg)
         self.layers = []
         for lw in weights[:-1]:
@@ -89,11 +94,19 @@ class Encoder:
             for k, v in lw.items():
                 # torch W (out,in) -> t(W) made dense: torch (in,out) == reference (out,in) column-major
                 dev[k] = ctx.toback(np.ascontiguousarray(v.T) if v.ndim == 2 else v)
+            if fused:
+                wqkv = np.concatenate([lw["wq"], lw["wk"], lw["wv"]], axis=0)            # torch (3d, d)
+                bqkv = np.concatenate([lw["bq"], np.zeros_like(lw["bq"]), lw["bv"]])     # k has no bias
+                dev["wqkv"] = ctx.toback(np.ascontiguousarray(wqkv.T))
+                dev["bqkv"] = ctx.toback(bqkv)
+                for k in ("wq", "wk", "wv", "bq", "bv"):
+                    del dev[k]
             self.layers.append(dev)
         self.final = {k: ctx.toback(v) for k, v in weights[-1].items()}
         d, f, L = cfg.d_model, cfg.ffn, cfg.tokens
         al = lambda n: (n + 255) // 256 * 256
         sizes = dict(xin=d * L * 2, x=d * L * 2, h=d * L * 2, q=d * L * 2, k=d * L * 2, v=d * L * 2, att=d * L * 2, att_t=d * L * 2,
+                     qkv=3 * d * L * 2,
                      f=f * L * 2, y=d * L * 2, mean=L * 4, rstd=L * 4)
         self.slab = ctx.allocate(np.uint8, sum(al(s) for s in sizes.values()))
         off = 0
@@ -134,6 +147,8 @@ class Encoder:
         scale = 1.0 / sqrt(E)
         as_heads = lambda t: t.reshape(E, H, L, 1).permute((0, 2, 1, 3))   # (E,L,H,B) view, no copy
         ctx.copy(x, self.xin)
+        if self.fused:
+            return self._forward_fused(x, h, att_t, ff, mean, rstd, scale)
         for w in self.layers:
             ctx.ws.reset()
             layernorm_(ctx, h, mean, rstd, x, w["ln1_g"], w["ln1_b"], d, c.eps)
@@ -152,6 +167,35 @@ class Encoder:
             if c.clamp:
                 clamp_(ctx, x, x, -F16_MAX, F16_MAX)
         layernorm_(ctx, self.y, mean, rstd, x, self.final["lnf_g"], self.final["lnf_b"], d, c.eps)
+        return self.y
+
+    def _forward_fused(self, x, h, att_t, ff, mean, rstd, scale) -> DeviceArray:
+        c, ctx = self.cfg, self.ctx
+        d, f, L, H, E = c.d_model, c.ffn, c.tokens, c.heads, c.head_dim
+        qkv = self._buf("qkv", np.float16, 3 * d, L)
+        esz = 2
+
+        def head_view(i):  # rows [i*d, (i+1)*d) of qkv seen as (E, L, H, 1)
+            return DeviceArray(ctx, qkv.ptr + i * d * esz, np.float16, (E, L, H, 1), (1, 3 * d, E, 3 * d * L), owner=qkv)
+
+        # token-major destination for sdpa: (E, L, H, 1) view of the (d, L) buffer the o-projection reads
+        att_view = DeviceArray(ctx, att_t.ptr, np.float16, (E, L, H, 1), (1, d, E, d * L), owner=att_t)
+        clamp = (-F16_MAX, F16_MAX) if c.clamp else None
+        first = self.layers[0]
+        layernorm_(ctx, h, mean, rstd, x, first["ln1_g"], first["ln1_b"], d, c.eps)
+        for i, w in enumerate(self.layers):
+            ctx.ws.reset()
+            matmul_(ctx, qkv, w["wqkv"], h, w["bqkv"])
+            sdpa(ctx, head_view(0), head_view(1), head_view(2), None, scale, out=att_view)
+            matmul_(ctx, h, w["wo"], att_t, w["bo"])
+            add_layernorm_(ctx, h, mean, rstd, x, h, w["ln2_g"], w["ln2_b"], d, c.eps)          # x += o; h = LN2(x)
+            matmul_(ctx, ff, w["w1"], h, w["b1"], epi="gelu")
+            matmul_(ctx, h, w["w2"], ff, w["b2"])
+            if i + 1 < len(self.layers):
+                g, b, dst = self.layers[i + 1]["ln1_g"], self.layers[i + 1]["ln1_b"], h
+            else:
+                g, b, dst = self.final["lnf_g"], self.final["lnf_b"], self.y
+            add_layernorm_(ctx, dst, mean, rstd, x, h, g, b, d, c.eps, clamp=clamp)             # x = clamp(x + g); LN
         return self.y
 
     def capture(self):

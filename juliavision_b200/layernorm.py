@@ -30,6 +30,23 @@ def layernorm_(ctx: Ctx, out: DeviceArray, mean: DeviceArray, rstd: DeviceArray,
     return out
 
 
+def add_layernorm_(ctx: Ctx, out: DeviceArray, mean: DeviceArray, rstd: DeviceArray, x: DeviceArray, h: DeviceArray,
+                   gamma: Optional[DeviceArray], beta: Optional[DeviceArray], C: int, eps: float,
+                   clamp: Optional[tuple] = None) -> DeviceArray:
+    """x .= clamp(x .+ h); layernorm!(out, mean, rstd, x, ...) as one launch (fp16). The same values
+    as add.Tensor, clamp.default and native_layer_norm run one after another."""
+    for a in (x, h, out):
+        if not a.isdense() or a.dtype != np.float16 or a.size != x.size:
+            raise B200Error(16, "add_layernorm!: x, h, out must be dense fp16 arrays of one size")
+    groups = x.size // C
+    lo, hi = clamp if clamp is not None else (0.0, 0.0)
+    check(_lib.lib().b200_add_layernorm_f16(ctx.handle, groups, C, x.ptr, h.ptr, int(clamp is not None), float(lo),
+                                            float(hi), out.ptr, mean.ptr, rstd.ptr,
+                                            gamma.ptr if gamma is not None else None,
+                                            beta.ptr if beta is not None else None, float(eps)))
+    return out
+
+
 def native_layer_norm(ctx: Ctx, a: DeviceArray, nshape, gamma=None, beta=None, eps: float = 1e-5, out_dtype=None):
     """The fast branch of runop!(native_layer_norm.default) (ops.jl:575-609): normalised dims are
     the leading ones; returns (out, mean, rstd)."""

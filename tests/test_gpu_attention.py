@@ -58,6 +58,24 @@ def test_interleaved_heads(ctx, ora):
     assert relerr(got, ref) < TOL, describe(got, ref, TOL)
 
 
+def test_token_major_output_view(ctx, ora):
+    """out given as an (E,L,H,B) view of a token-major buffer: the permute copy after sdpa is folded
+    into the store; values are those of the dense call."""
+    from .gpu_helpers import qkv_views
+    rng = np.random.default_rng(13)
+    B, H, L, E = 2, 5, 200, 64
+    q, k, v = (np.float16(rng.standard_normal((B, H, L, E))) for _ in range(3))
+    dq, dk, dv = qkv_views(ctx, q, k, v)
+    dense, _ = attention_gpu(ctx, q, k, v, 0.125)
+    buf = ctx.allocate(np.float16, E * H, L, B)                     # torch (B, L, H*E)
+    ctx.fill_bytes(buf, 0xFF)
+    view = jv.DeviceArray(ctx, buf.ptr, np.float16, (E, L, H, B), (1, E * H, E, E * H * L), owner=buf)
+    jv.sdpa(ctx, dq, dk, dv, None, 0.125, out=view)
+    ctx.synchronize()
+    got = buf.to_host().reshape(B, L, H, E).transpose(0, 2, 1, 3)
+    assert np.array_equal(got, dense)
+
+
 def test_head_dim_beyond_one_swizzle_row_takes_the_scalar_kernel(ctx, ora):
     rng = np.random.default_rng(12)
     q, k, v = (np.float16(rng.standard_normal((1, 2, 64, 72)) * 0.2) for _ in range(3))  # test_flash.jl:36

@@ -10,9 +10,9 @@ from .gpu_helpers import describe
 pytestmark = pytest.mark.gpu
 
 
-def _run(ctx, cfg, x, graph=False):
+def _run(ctx, cfg, x, graph=False, fused=True):
     w = init_weights(cfg)
-    enc = Encoder(ctx, cfg, w)
+    enc = Encoder(ctx, cfg, w, fused=fused)
     ctx.upload(enc.xin, x)
     if graph:
         g = enc.capture()
@@ -33,6 +33,36 @@ def test_two_layer_prefix_vs_oracle(ctx):
     ref = oracle_forward(cfg, w, x)
     assert got.shape == (cfg.tokens, cfg.d_model)
     assert relerr(got, ref) < 1e-2, describe(got, ref, 1e-2)
+
+
+def test_fused_rewrites_change_no_value(ctx):
+    """qkv in one GEMM, token-major sdpa store and add(+clamp)+LN in one launch are rewrites, not
+    approximations: the pass must give the op-by-op result bit for bit."""
+    cfg = EncoderConfig(layers=2, d_model=256, heads=4, ffn=1024, tokens=300)
+    x = np.float16(np.random.default_rng(4).standard_normal((cfg.tokens, cfg.d_model)))
+    _, _, plain = _run(ctx, cfg, x, fused=False)
+    _, _, fused = _run(ctx, cfg, x, fused=True)
+    assert np.array_equal(plain, fused)
+
+
+def test_add_layernorm_equals_the_three_ops(ctx):
+    rng = np.random.default_rng(5)
+    for groups, C in ((300, 256), (77, 1280), (5, 100)):
+        x0 = np.float16(rng.standard_normal((groups, C)) * 300)
+        h0 = np.float16(rng.standard_normal((groups, C)) * 300)
+        g = np.float16(1 + 0.1 * rng.standard_normal(C))
+        b = np.float16(0.1 * rng.standard_normal(C))
+        dg, db = ctx.toback(g), ctx.toback(b)
+        mean, rstd = ctx.allocate(np.float32, groups), ctx.allocate(np.float32, groups)
+        xa, ha, oa = ctx.toback(x0), ctx.toback(h0), ctx.allocate(np.float16, C, groups)
+        jv.add_(ctx, xa, xa, ha)
+        jv.clamp_(ctx, xa, xa, -500.0, 500.0)
+        jv.layernorm_(ctx, oa, mean, rstd, xa, dg, db, C, 1e-5)
+        xb, hb, ob = ctx.toback(x0), ctx.toback(h0), ctx.allocate(np.float16, C, groups)
+        jv.add_layernorm_(ctx, ob, mean, rstd, xb, hb, dg, db, C, 1e-5, clamp=(-500.0, 500.0))
+        ctx.synchronize()
+        assert np.array_equal(xa.to_host(), xb.to_host())
+        assert np.array_equal(oa.to_host(), ob.to_host())
 
 
 def test_graph_replay_equals_eager(ctx):
