@@ -353,6 +353,14 @@ int b200_workspace_stats(b200_ctx* c, size_t* used, size_t* cap, int* retired) {
     return B200_OK;
 }
 
+// Development aid, not part of the public header: point the GEMM timeline at a device buffer of
+// at least 32 uint64 slots (or null to stop).
+int b200_internal_gemm_trace(b200_ctx* c, void* dptr) {
+    B200_REQUIRE(c, B200_EINVAL, "gemm_trace: null ctx");
+    c->gemm_trace = static_cast<unsigned long long*>(dptr);
+    return B200_OK;
+}
+
 int b200_shard_range(int64_t total, int world, int rank, int64_t align, int64_t* begin, int64_t* end) {
     B200_REQUIRE(begin && end && world > 0 && rank >= 0 && rank < world && total >= 0 && align > 0,
                  B200_EINVAL, "shard_range: bad argument");

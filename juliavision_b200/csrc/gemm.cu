@@ -12,11 +12,11 @@
 // Replaces matmul_coopmat! + Lava.coopmat_gemm! + padcols_kernel! + mm_epilogue_kernel!
 // (reference kernels/extern/matmul.jl:172-273).
 //
-// Roles inside one persistent CTA (192 threads):
+// Roles inside one persistent CTA (320 threads):
 //   warp 0    TMA producer  (one lane)        global -> shared ring, STAGES deep
 //   warp 1    UMMA issuer   (one lane)        shared -> TMEM accumulators (two, ping-pong)
-//   warps 2-5 epilogue      (128 threads)     TMEM -> registers -> +bias, round, act ->
-//                                             16-byte stores straight to global memory
+//   warps 2-9 epilogue      (256 threads)     TMEM -> registers -> +bias, round, act ->
+//                                             warp-private shared slab -> coalesced 16-byte stores
 #include <cuda_fp16.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -28,7 +28,8 @@ namespace b200 {
 
 constexpr int GEMM_BM = 128; // tokens per CTA (TMEM lanes)
 constexpr int GEMM_BK = 64;  // one 128-byte swizzle row of fp16
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS; // producer warp, UMMA warp, epilogue warps
 constexpr int SMEM_LIMIT = 232448; // 227 KB
 
 // NCTA = 1: one CTA per tile of 128 tokens x BN features (tcgen05.mma.cta_group::1).
@@ -42,7 +43,8 @@ template <int BN, typename OutT, int NCTA> struct GemmCfg {
     static constexpr int B_BYTES = B_COLS * GEMM_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int OUT_COLS = 128 / (int)sizeof(OutT); // columns per 128-byte staging row
-    static constexpr int TAIL_BYTES = 4 * BN * 2 + 256; // per-warp fp16 bias + barriers
+    static constexpr int SUB_COLS = 64 / (int)sizeof(OutT);   // epilogue slab: 64 bytes of output per row
+    static constexpr int TAIL_BYTES = EPI_WARPS * (BN * 2 + 2048) + 256; // per-warp fp16 bias and slab, barriers
     static constexpr int STAGES_RAW = (SMEM_LIMIT - TAIL_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TAIL_BYTES;
@@ -64,7 +66,15 @@ template <typename OutT> struct GemmParams {
     int bias_per_n;        // 0: bias[i] over features (M); 1: bias[j] over tokens (N)
     int epilogue;
     int* d_status;
+    unsigned long long* trace;  // optional timeline of worker 0 (globaltimer ns), null in normal use
 };
+
+// Timeline slots written by worker 0 when tracing: a development aid for reading where a launch
+// spends its time; costs one predictable branch per event otherwise.
+#define GEMM_TRACE(slot)                                                   \
+    do {                                                                   \
+        if (p.trace != nullptr && worker == 0 && rank == 0) p.trace[(slot)] = globaltimer_ns(); \
+    } while (0)
 
 __device__ __forceinline__ float erf_as(float x) {
     // Abramowitz & Stegun 7.1.26 in fp32, the reference's erf (ops.jl:161-169).
@@ -74,10 +84,23 @@ __device__ __forceinline__ float erf_as(float x) {
                       0.254829592f) * t * __expf(-a * a);
     return x < 0.f ? -y : y;
 }
+// geluexact on the fp16-rounded value: 0.5 x (1 + erf(x/sqrt2)), A&S erf, fp32 (ops.jl:1665-1670).
+__device__ __forceinline__ float gelu_exact(float x) {
+    const float z = x * 0.70710678118654752f;
+    const float a = fabsf(z);
+    float t;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, a, 1.0f)));
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-a * a * 1.4426950408889634f));
+    const float poly = ((((1.061405429f * t - 1.453152027f) * t + 1.421413741f) * t - 0.284496736f) * t + 0.254829592f) * t;
+    const float y = fmaf(-poly, e, 1.0f);          // erf(|z|)
+    const float hx = 0.5f * x;
+    return fmaf(hx, copysignf(y, z), hx);
+}
 __device__ __forceinline__ float apply_act(int epi, float v) {
     switch (epi) {
         case B200_EPI_RELU: return fmaxf(v, 0.f);
-        case B200_EPI_GELU: return 0.5f * v * (1.0f + erf_as(v * 0.70710678118654752f));
+        case B200_EPI_GELU: return gelu_exact(v);
         case B200_EPI_GELU_TANH: {
             float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
             return 0.5f * v * (1.0f + tanhf(u));
@@ -103,7 +126,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         return;
     }
     __half* sbias = reinterpret_cast<__half*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sbias) + 4 * BN * 2);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sbias) + EPI_WARPS * (BN * 2 + 2048));
     uint64_t* full = bars;                     // [STAGES]  (pair: only the leader's are used)
     uint64_t* empty = bars + Cfg::STAGES;      // [STAGES]
     uint64_t* tfull = bars + 2 * Cfg::STAGES;  // [2]
@@ -118,13 +141,14 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
     const int64_t nworkers = NCTA == 2 ? (gridDim.x >> 1) : gridDim.x;
 
     if (threadIdx.x == 0) {
+        GEMM_TRACE(0); // kernel entry
         for (int s = 0; s < Cfg::STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tfull[a], 1);
-            mbar_init(&tempty[a], 4 * NCTA);
+            mbar_init(&tempty[a], EPI_WARPS * NCTA);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -147,6 +171,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
     const uint32_t tmem_base = *tmem_slot;
 
     const int64_t tiles_per_batch = (int64_t)p.tiles_m * p.tiles_n;
+    if (threadIdx.x == 0) GEMM_TRACE(1); // setup done
 
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer
@@ -184,6 +209,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                     }
                     if (++s == Cfg::STAGES) { s = 0; ph ^= 1; }
                 }
+                GEMM_TRACE(2); // producer: last load of a tile issued (overwritten per tile)
             }
         }
     } else if (warp == 1) {
@@ -215,6 +241,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         break;
                     }
                     tc_fence_after();
+                    if (kb == 0 && it == 0) GEMM_TRACE(3); // first stage landed
                     const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
                     const uint32_t b_addr = a_addr + Cfg::A_BYTES;
 #pragma unroll
@@ -234,16 +261,22 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                     if constexpr (NCTA == 2) umma_commit_pair(&tfull[acc], 3);
                     else umma_commit(&tfull[acc]);
                 }
+                GEMM_TRACE(4 + (it < 4 ? it : 3)); // all UMMAs of tile `it` issued
             }
         }
     } else {
         // ---------------------------------------------------------------- epilogue
-        // Each warp owns the 32 token rows of its TMEM lane quadrant end to end: its own bias copy,
-        // its own two staging slabs (32 rows x 128 B) and its own TMA stores, so the four warps
-        // never wait for one another.
-        const int ew = warp - 2;               // 0..3
+        // Eight warps, two per TMEM lane quadrant; the two of a quadrant take alternate slabs of
+        // SUB columns.  Per slab: TMEM -> registers -> +bias, round, activation -> a warp-private
+        // swizzled shared slab (32 rows x 64 B) -> read back transposed so that four lanes cover 64
+        // contiguous bytes of one output row -> 16-byte global stores.  Warps never wait for one
+        // another and nothing is left in flight that a later step would have to wait for.
+        constexpr int SUB = Cfg::SUB_COLS;     // columns per slab: 64 bytes of output per row
+        const int ew = warp - 2;               // 0..7
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
+        const int half = ew >> 2;              // which alternate slabs
         const int row = quad * 32 + lane;      // token row inside this CTA's half of the tile
+        uint8_t* wstg = reinterpret_cast<uint8_t*>(sbias + EPI_WARPS * BN) + ew * 2048;
         __half* wbias = sbias + ew * BN;
         int64_t it = 0;
         for (int64_t tile = worker; tile < p.total_tiles; tile += nworkers, ++it) {
@@ -262,30 +295,33 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             const bool got = mbar_wait(&tfull[acc], aph, p.d_status, KST_WAIT_TMEM_FULL, abort_flag);
             if (__any_sync(0xffffffffu, !got)) break; // one answer per warp
             tc_fence_after();
+            if (ew == 0 && lane == 0) GEMM_TRACE(8 + (it < 4 ? it : 3)); // accumulator of tile `it` ready
 
-            constexpr int NCHUNK = BN / Cfg::OUT_COLS;
+            OutT* gtile = p.out + (size_t)batch * p.strideO + (size_t)(n0 + quad * 32) * p.ldo + m0;
+            const int rows_valid = (int)(p.N - (n0 + quad * 32));   // rows of this warp's slab inside the output
+            constexpr int NSLAB = BN / SUB / 2;
 #pragma unroll 1
-            for (int c = 0; c < NCHUNK; ++c) {
-                const int col0 = c * Cfg::OUT_COLS;
-                float v[Cfg::OUT_COLS];
+            for (int i = 0; i < NSLAB; ++i) {
+                const int col0 = (2 * i + half) * SUB;
+                float v[SUB];
                 {
                     const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN + col0;
-                    uint32_t r0[32];
-                    tmem_ld32(taddr, r0);
-                    if constexpr (Cfg::OUT_COLS == 64) {
-                        uint32_t r1[32];
-                        tmem_ld32(taddr + 32, r1);
+                    if constexpr (SUB == 32) {
+                        uint32_t r[32];
+                        tmem_ld32(taddr, r);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[32 + i] = __uint_as_float(r1[i]) + rbias;
+                        for (int t = 0; t < 32; ++t) v[t] = __uint_as_float(r[t]) + rbias;
                     } else {
+                        uint32_t r[16];
+                        tmem_ld16(taddr, r);
                         tmem_wait_ld();
-                    }
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r0[i]) + rbias;
+                        for (int t = 0; t < 16; ++t) v[t] = __uint_as_float(r[t]) + rbias;
+                    }
                 }
-                if (c == NCHUNK - 1) {
-                    // Accumulator fully read: hand it back to the UMMA issuer (in the leader CTA).
+                if (i == NSLAB - 1) {
+                    // This warp has read all it needs of the accumulator: hand it back (leader CTA).
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {
@@ -293,58 +329,79 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         else mbar_arrive(&tempty[acc]);
                     }
                 }
-                const int tok = n0 + row;
-                if (m0 + col0 >= p.M || tok >= p.N) continue; // nothing of this row chunk is inside the output
+                if (m0 + col0 >= p.M || rows_valid <= 0) continue; // slab entirely outside the output
 
-                // Straight from registers to global memory: each thread owns OUT_COLS consecutive
-                // features of one token, i.e. 128 contiguous bytes, written as 16-byte vectors.  No
-                // staging and no completion to wait for, which is what a tile with a short K loop
-                // (where nothing hides the epilogue) needs.
-                OutT* gout = p.out + (size_t)batch * p.strideO + (size_t)tok * p.ldo + (m0 + col0);
-                const int valid = (int)(p.M - (m0 + col0)) < Cfg::OUT_COLS ? (int)(p.M - (m0 + col0)) : Cfg::OUT_COLS;
+                // registers -> shared, lane = row; 16-byte piece j of row r sits at piece j ^ ((r>>1)&3)
+                uint8_t* rowp = wstg + lane * 64;
+                const int sw = (lane >> 1) & 3;
                 if constexpr (sizeof(OutT) == 2) {
+                    auto emit = [&](auto act) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        uint4 o;
-                        __half2* h = reinterpret_cast<__half2*>(&o);
+                        for (int j = 0; j < 4; ++j) {
+                            uint4 o;
+                            __half2* h = reinterpret_cast<__half2*>(&o);
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int cidx = j * 8 + q * 2;
-                            // Round to fp16 first; the activation sees the rounded value.
-                            const float2 bb = __half22float2(*reinterpret_cast<const __half2*>(&wbias[col0 + cidx]));
-                            __half2 t = __floats2half2_rn(v[cidx] + bb.x, v[cidx + 1] + bb.y);
-                            if (p.epilogue != B200_EPI_NONE) {
-                                float2 f = __half22float2(t);
-                                t = __floats2half2_rn(apply_act(p.epilogue, f.x), apply_act(p.epilogue, f.y));
+                            for (int q = 0; q < 4; ++q) {
+                                const int cidx = j * 8 + q * 2;
+                                const float2 bb = __half22float2(*reinterpret_cast<const __half2*>(&wbias[col0 + cidx]));
+                                // Round to fp16 first; the activation sees the rounded value.
+                                __half2 t = __floats2half2_rn(v[cidx] + bb.x, v[cidx + 1] + bb.y);
+                                h[q] = act(t);
                             }
-                            h[q] = t;
+                            *reinterpret_cast<uint4*>(rowp + ((j ^ sw) << 4)) = o;
                         }
-                        if (j * 8 + 8 <= valid) {
-                            *reinterpret_cast<uint4*>(gout + j * 8) = o;
-                        } else {
-                            const __half* e = reinterpret_cast<const __half*>(&o);
-                            for (int t = 0; t < 8; ++t)
-                                if (j * 8 + t < valid) gout[j * 8 + t] = e[t];
-                        }
+                    };
+                    switch (p.epilogue) {
+                        case B200_EPI_RELU: emit([](__half2 t) { return __hmax2(t, __float2half2_rn(0.f)); }); break;
+                        case B200_EPI_GELU:
+                            emit([](__half2 t) {
+                                const float2 f = __half22float2(t);
+                                return __floats2half2_rn(gelu_exact(f.x), gelu_exact(f.y));
+                            });
+                            break;
+                        case B200_EPI_GELU_TANH:
+                            emit([](__half2 t) {
+                                const float2 f = __half22float2(t);
+                                return __floats2half2_rn(apply_act(B200_EPI_GELU_TANH, f.x), apply_act(B200_EPI_GELU_TANH, f.y));
+                            });
+                            break;
+                        default: emit([](__half2 t) { return t; }); break;
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
+                    for (int j = 0; j < 4; ++j) {
                         float4 o;
                         o.x = apply_act(p.epilogue, v[j * 4 + 0] + __half2float(wbias[col0 + j * 4 + 0]));
                         o.y = apply_act(p.epilogue, v[j * 4 + 1] + __half2float(wbias[col0 + j * 4 + 1]));
                         o.z = apply_act(p.epilogue, v[j * 4 + 2] + __half2float(wbias[col0 + j * 4 + 2]));
                         o.w = apply_act(p.epilogue, v[j * 4 + 3] + __half2float(wbias[col0 + j * 4 + 3]));
-                        if (j * 4 + 4 <= valid) {
-                            *reinterpret_cast<float4*>(gout + j * 4) = o;
+                        *reinterpret_cast<float4*>(rowp + ((j ^ sw) << 4)) = o;
+                    }
+                }
+                __syncwarp();
+                // shared -> global, four lanes per row: lane l moves piece l%4 of rows l/4, l/4+8, ...
+                constexpr int EPP = 16 / (int)sizeof(OutT);  // elements per 16-byte piece
+                const int pj = lane & 3;
+                const int colp = col0 + pj * EPP;             // first feature column of this lane's piece
+                const int cvalid = (int)(p.M - m0) - colp;    // columns of the piece inside the output
+#pragma unroll
+                for (int rr = 0; rr < 4; ++rr) {
+                    const int r = (lane >> 2) + 8 * rr;
+                    const uint4 piece = *reinterpret_cast<const uint4*>(wstg + r * 64 + ((pj ^ ((r >> 1) & 3)) << 4));
+                    if (r < rows_valid && cvalid > 0) {
+                        OutT* g = gtile + (size_t)r * p.ldo + colp;
+                        if (cvalid >= EPP) {
+                            *reinterpret_cast<uint4*>(g) = piece;
                         } else {
-                            const float* e = reinterpret_cast<const float*>(&o);
-                            for (int t = 0; t < 4; ++t)
-                                if (j * 4 + t < valid) gout[j * 4 + t] = e[t];
+                            const OutT* e = reinterpret_cast<const OutT*>(&piece);
+                            for (int t = 0; t < EPP; ++t)
+                                if (t < cvalid) g[t] = e[t];
                         }
                     }
                 }
+                __syncwarp(); // the slab is free for the next round
             }
+            if (ew == 0 && lane == 0) GEMM_TRACE(12 + (it < 4 ? it : 3)); // epilogue of tile `it` done
         }
     }
 
@@ -361,6 +418,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         if constexpr (NCTA == 2) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
         else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
+    if (threadIdx.x == 0) GEMM_TRACE(16); // exit
 }
 
 // Scalar path for operands the tensor maps cannot express (unaligned pointers or leading
@@ -463,6 +521,7 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
     p.bias_per_n = bias_per_n;
     p.epilogue = epi;
     p.d_status = ctx->d_status;
+    p.trace = ctx->gemm_trace;
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;

@@ -47,6 +47,7 @@ struct b200_ctx {
     int* d_status = nullptr;   // device status words: [0] first failed wait code
     int64_t launches = 0;
     bool capturing = false;
+    unsigned long long* gemm_trace = nullptr;  // device buffer of >= 32 slots while tracing, else null
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     b200::EncodeTiledFn encode = nullptr;
 
