@@ -13,14 +13,8 @@
 // (flash.jl:725,765), O accumulates in fp32, and a row whose sum is zero divides by one
 // (flash.jl:1015).
 //
-// One CTA owns 128 queries of one (head, batch) and walks the keys in blocks of 128.
-//   warp 0    TMA producer: Q once, then K and V tiles through a two-stage ring
-//   warp 1    UMMA issuer:  S = Q K'  (128x128x64),  O += P V  (128xEPx128)
-//   warps 2-5 softmax: one thread per query row; TMEM -> registers, running max / sum,
-//             P as fp16 into swizzled shared memory, O rescaled in TMEM when the max moved,
-//             and at the end O / l written to global memory.
-// Two CTAs share an SM (256 TMEM columns and ~113 KB of shared memory each), so one CTA's
-// softmax overlaps the other's tensor-core work.
+// One CTA owns 256 queries (two tiles of 128) of one (head, batch) and walks the keys in blocks
+// of 128; the kernel comment below gives the roles and the pipeline.
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -28,16 +22,27 @@
 
 namespace b200 {
 
-constexpr int ATT_BR = 128;  // queries per CTA (TMEM lanes)
+constexpr int ATT_BR = 128;  // queries per tile (TMEM lanes); a CTA owns two tiles
 constexpr int ATT_BC = 128;  // keys per block
 constexpr int ATT_EP = 64;   // head dim padded to one 128-byte swizzle row
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_ON = 80;   // P V accumulator columns: 64 of O, then the row sum in column 64
+constexpr int ATT_THREADS = 384;  // warps 0-3, 4-7: softmax of tile 0, 1; warp 8: TMA; warps 9, 10: UMMA; 11 idle
 constexpr int ATT_TILE_BYTES = 128 * 128; // every operand tile is 128 rows x 128 B
-constexpr int ATT_SMEM_TILES = 1 /*Q*/ + 4 /*K,V x2*/ + 2 /*P*/;
-constexpr int ATT_SMEM_BYTES = ATT_SMEM_TILES * ATT_TILE_BYTES + 256 /*barriers*/ + 768 /*align slack*/;
-constexpr int ATT_TMEM_COLS = 256;
-constexpr int ATT_S_COL = 0;    // S: 128 fp32 columns
-constexpr int ATT_O_COL = 128;  // O: EP fp32 columns
+constexpr int ATT_KV_STAGES = 3;
+#ifndef ATT_TURN_AT
+#define ATT_TURN_AT 1   // after which quarter (0..3) of its exponentials a tile passes the turn
+#endif
+// shared-memory map, in 16 KB tiles
+constexpr int ATT_T_Q = 0;                         // 2 tiles
+constexpr int ATT_T_K = 2;                         // 3 tiles
+constexpr int ATT_T_V = ATT_T_K + ATT_KV_STAGES;   // 3 tiles
+constexpr int ATT_T_ONES = ATT_T_V + ATT_KV_STAGES; // 1 tile: the column of ones that makes P V emit row sums
+constexpr int ATT_T_P = ATT_T_ONES + 1;            // 2 x 2 tiles
+constexpr int ATT_T_END = ATT_T_P + 4;
+constexpr int ATT_SMEM_BYTES = ATT_T_END * ATT_TILE_BYTES + 256;
+constexpr int ATT_TMEM_COLS = 512;
+constexpr int ATT_S_COL = 0;    // S of tile t at columns [128 t, 128 t + 128)
+constexpr int ATT_O_COL = 256;  // O of tile t at columns [256 + 128 t, ... + 80)
 
 struct AttnParams {
     int E, Lq, Lk, H, B;
@@ -46,142 +51,195 @@ struct AttnParams {
     int64_t osL, osH, osB;  // element strides of out along L, H, B (E is contiguous)
     int out_f32;
     int* d_status;
+    unsigned long long* trace;  // optional timeline of CTA (0,0,0) (globaltimer ns), null in normal use
 };
+
+#define ATT_TRACE(slot)                                                                              \
+    do {                                                                                             \
+        if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 128) \
+            p.trace[(slot)] = globaltimer_ns();                                                      \
+    } while (0)
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// 2^lo, 2^hi as one packed fp16x2 (lo in the low half).  The packed MUFU form
+// (ex2.approx.f16x2) measured slower than two fp32 ex2 plus one pack on this part.
+__device__ __forceinline__ uint32_t ex2_pack_f16x2(float lo, float hi) {
+    __half2 h2 = __floats2half2_rn(ex2(lo), ex2(hi));
+    return *reinterpret_cast<uint32_t*>(&h2);
+}
+__device__ __forceinline__ void tmem_st16_raw(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 
-__global__ void __launch_bounds__(ATT_THREADS, 2)
+// One CTA = 256 queries (two tiles of 128) of one (head, batch), one CTA per SM:
+//   warps 0-3  softmax of tile 0, warps 4-7 softmax of tile 1: one thread per query row, the whole
+//              128-score row in registers (these two warpgroups take registers from the third)
+//   warp 8     TMA producer: both Q tiles once, then K and V blocks through 3-stage rings
+//   warps 9,10 UMMA issuers, one lane per tile: S_t = Q_t K' and O_t += P_t [V | 1] per key block;
+//              the two chains are independent, so the tensor core works on one tile while the
+//              other tile's softmax runs
+// The extra "ones" column appended to V makes the tensor core accumulate the softmax denominator
+// (in fp32, from the same fp16-rounded P the numerator uses), so the softmax threads spend their
+// instructions on max / exp only, and exp runs two-wide (ex2.approx.f16x2).
+__global__ void __launch_bounds__(ATT_THREADS, 1)
 attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                         const __grid_constant__ CUtensorMap tmapK,
                         const __grid_constant__ CUtensorMap tmapV, const AttnParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                               ~uintptr_t(1023));
-    uint8_t* sQ = smem;
-    uint8_t* sKV = smem + ATT_TILE_BYTES;          // [stage][K|V]
-    uint8_t* sP = smem + 5 * ATT_TILE_BYTES;       // two 64-key halves
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * ATT_TILE_BYTES);
-    uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;   // [2]
-    uint64_t* k_empty = bars + 3;  // [2]
-    uint64_t* v_full = bars + 5;   // [2]
-    uint64_t* v_empty = bars + 7;  // [2]
-    uint64_t* s_full = bars + 9;
-    uint64_t* s_empty = bars + 10;
-    uint64_t* p_full = bars + 11;
-    uint64_t* pv_done = bars + 12;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    extern __shared__ __align__(1024) uint8_t smem[];
+    // Uniform across the grid: a base that is not 1024-aligned makes every thread leave before
+    // any barrier or TMEM allocation exists.
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicCAS(p.d_status, 0, KST_SMEM_LAYOUT);
+        return;
+    }
+    auto tile_ptr = [&](int t) { return smem + t * ATT_TILE_BYTES; };
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_T_END * ATT_TILE_BYTES);
+    uint64_t* q_full = bars + 0;    // [2]
+    uint64_t* k_full = bars + 2;    // [3]
+    uint64_t* k_empty = bars + 5;   // [3]
+    uint64_t* v_full = bars + 8;    // [3]
+    uint64_t* v_empty = bars + 11;  // [3]
+    uint64_t* s_full = bars + 14;   // [2]
+    uint64_t* s_empty = bars + 16;  // [2]
+    uint64_t* p_full = bars + 18;   // [2]
+    uint64_t* pv_done = bars + 20;  // [2]
+    uint64_t* exp_turn = bars + 22; // [2]: whose turn it is to run its exponentials
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * ATT_BR;
+    const int q0 = blockIdx.x * (2 * ATT_BR);
     const int h = blockIdx.y;
     const int b = blockIdx.z;
     const int nblk = (p.Lk + ATT_BC - 1) / ATT_BC;
+    const int ntiles = (q0 + ATT_BR < p.Lq) ? 2 : 1;   // the second tile may lie wholly past Lq
 
-    // The carve-up above needs the aligned base to leave room for every tile; the test is
-    // uniform across the CTA, so a misplaced base makes every thread leave before any
-    // barrier or TMEM allocation exists.
-    if (smem + 7 * ATT_TILE_BYTES + 256 > smem_raw + ATT_SMEM_BYTES) {
-        if (threadIdx.x == 0) atomicCAS(p.d_status, 0, KST_SMEM_LAYOUT);
-        return;
-    }
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&k_full[s], 1);
-            mbar_init(&k_empty[s], 1);
-            mbar_init(&v_full[s], 1);
-            mbar_init(&v_empty[s], 1);
+        ATT_TRACE(0);
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&q_full[t], 1);
+            mbar_init(&s_full[t], 1);
+            mbar_init(&s_empty[t], 4);   // one arrival per softmax warp
+            mbar_init(&p_full[t], 4);
+            mbar_init(&pv_done[t], 1);
+            mbar_init(&exp_turn[t], 4);
         }
-        mbar_init(s_full, 1);
-        mbar_init(s_empty, 128);
-        mbar_init(p_full, 128);
-        mbar_init(pv_done, 1);
+        for (int s = 0; s < ATT_KV_STAGES; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], ntiles);   // freed when every tile's issuer is done with it
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], ntiles);
+        }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tmapQ);
         prefetch_tmap(&tmapK);
         prefetch_tmap(&tmapV);
     }
-    if (warp == 1) {
+    if (warp == 8) {
         tmem_alloc(tmem_slot, ATT_TMEM_COLS);
         tmem_relinquish();
+    }
+    if (warp < 4) {
+        // The ones tile, in the MN-major 128-byte-swizzled form of a V tile: key row r is 128 B,
+        // logical 16-byte piece 0 (columns 0..7) sits at physical piece (0 ^ (r & 7)).
+        const int r = warp * 32 + lane;
+        uint4* rowp = reinterpret_cast<uint4*>(tile_ptr(ATT_T_ONES) + r * 128);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) rowp[j] = make_uint4(0u, 0u, 0u, 0u);
+        rowp[r & 7] = make_uint4(0x00003C00u, 0u, 0u, 0u);   // fp16 1.0 in column 0
+        fence_proxy_async_smem();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
+    // Register budget: the two softmax warpgroups hold a full score row per thread; the third
+    // warpgroup (one TMA lane, one UMMA lane, two idle warps) needs almost nothing and hands its
+    // share over (setmaxnreg at the head of each role's branch).
+    if (warp == 11) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    } else if (warp == 8) {
         // ------------------------------------------------------------- TMA producer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, ATT_TILE_BYTES);
-            tma_load_4d(sQ, &tmapQ, q_full, 0, q0, h, b);
+            for (int t = 0; t < ntiles; ++t) {
+                mbar_arrive_expect_tx(&q_full[t], ATT_TILE_BYTES);
+                tma_load_4d(tile_ptr(ATT_T_Q + t), &tmapQ, &q_full[t], 0, q0 + t * ATT_BR, h, b);
+            }
             for (int j = 0; j < nblk; ++j) {
-                const int s = j & 1;
-                const uint32_t ph = (uint32_t)((j >> 1) & 1);
-                uint8_t* sk = sKV + (2 * s) * ATT_TILE_BYTES;
-                uint8_t* sv = sk + ATT_TILE_BYTES;
+                const int s = j % ATT_KV_STAGES;
+                const uint32_t ph = (uint32_t)((j / ATT_KV_STAGES) & 1);
                 if (!mbar_wait(&k_empty[s], ph ^ 1, p.d_status, KST_WAIT_EMPTY, abort_flag)) break;
                 mbar_arrive_expect_tx(&k_full[s], ATT_TILE_BYTES);
-                tma_load_4d(sk, &tmapK, &k_full[s], 0, j * ATT_BC, h, b);
+                tma_load_4d(tile_ptr(ATT_T_K + s), &tmapK, &k_full[s], 0, j * ATT_BC, h, b);
                 if (!mbar_wait(&v_empty[s], ph ^ 1, p.d_status, KST_WAIT_EMPTY, abort_flag)) break;
                 mbar_arrive_expect_tx(&v_full[s], ATT_TILE_BYTES);
-                tma_load_4d(sv, &tmapV, &v_full[s], 0, j * ATT_BC, h, b);
+                tma_load_4d(tile_ptr(ATT_T_V + s), &tmapV, &v_full[s], 0, j * ATT_BC, h, b);
             }
         }
-    } else if (warp == 1) {
-        // -------------------------------------------------------------- UMMA issuer
-        if (lane == 0) {
-            // S = Q K': both operands K-major (E contiguous).  O += P V: P K-major (keys
-            // contiguous per query row), V MN-major (E contiguous per key).
+    } else if (warp == 9 || warp == 10) {
+        // ------------------------------------------------------------- UMMA issuers
+        // One issuing lane per query tile (warp 9: tile 0, warp 10: tile 1).  Each walks its own
+        // chain  S_t(j+1) = Q_t K(j+1)'  as soon as the softmax has pulled S_t(j) into registers,
+        // then  O_t += P_t(j) [V(j) | 1]  once P_t(j) is written.  The two chains share only the
+        // K/V rings.  (Issuing a UMMA blocks while the tensor pipe is busy, so the issuing lanes
+        // are not softmax threads.)
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        const int t = warp - 9;
+        if (lane == 0 && t < ntiles) {
+            // S = Q K': both operands K-major (E contiguous).  O += P [V|1]: P K-major (keys
+            // contiguous per query row), V MN-major (E contiguous per key) with the ones tile as
+            // its second 64-column slab.
             constexpr uint32_t idesc_s = make_idesc_f16(ATT_BR, ATT_BC, 0, 0);
-            constexpr uint32_t idesc_o = make_idesc_f16(ATT_BR, ATT_EP, 0, 1);
+            constexpr uint32_t idesc_o = make_idesc_f16(ATT_BR, ATT_ON, 0, 1);
             constexpr uint64_t kdesc0 = make_smem_desc(16, 1024);
-            constexpr uint64_t vdesc0 = make_smem_desc(ATT_TILE_BYTES, 1024);
-            const uint32_t q_addr = smem_u32(sQ);
-            const uint32_t p_addr = smem_u32(sP);
-            const uint32_t s_tmem = tmem_base + ATT_S_COL;
-            const uint32_t o_tmem = tmem_base + ATT_O_COL;
+            const uint32_t ones_addr = smem_u32(tile_ptr(ATT_T_ONES));
+            const uint32_t q_addr = smem_u32(tile_ptr(ATT_T_Q + t));
+            const uint32_t p_addr = smem_u32(tile_ptr(ATT_T_P + 2 * t));
+            const uint32_t s_tmem = tmem_base + ATT_S_COL + t * 128;
+            const uint32_t o_tmem = tmem_base + ATT_O_COL + t * 128;
 
             auto issue_qk = [&](int j) -> bool {
-                const int s = j & 1;
-                const uint32_t ph = (uint32_t)((j >> 1) & 1);
-                if (!mbar_wait(&k_full[s], ph, p.d_status, KST_WAIT_FULL, abort_flag)) return false;
-                // S is single-buffered: block j may overwrite it once the softmax of block
-                // j-1 has read it out.
-                if (j > 0 && !mbar_wait(s_empty, (uint32_t)((j - 1) & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag))
+                const int sk = j % ATT_KV_STAGES;
+                if (!mbar_wait(&k_full[sk], (uint32_t)((j / ATT_KV_STAGES) & 1), p.d_status, KST_WAIT_FULL, abort_flag))
+                    return false;
+                if (j > 0 && !mbar_wait(&s_empty[t], (uint32_t)((j - 1) & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag))
                     return false;
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(sKV + (2 * s) * ATT_TILE_BYTES);
+                const uint32_t k_addr = smem_u32(tile_ptr(ATT_T_K + sk));
 #pragma unroll
                 for (int k = 0; k < ATT_EP / 16; ++k)
                     umma_ss(s_tmem, smem_desc_at(kdesc0, q_addr + k * 32), smem_desc_at(kdesc0, k_addr + k * 32),
                             idesc_s, k != 0);
-                umma_commit(&k_empty[s]);
-                umma_commit(s_full);
+                umma_commit(&s_full[t]);
+                umma_commit(&k_empty[sk]);   // one of `ntiles` arrivals that free this K stage
                 return true;
             };
 
-            bool ok = mbar_wait(q_full, 0, p.d_status, KST_WAIT_FULL, abort_flag);
+            bool ok = mbar_wait(&q_full[t], 0, p.d_status, KST_WAIT_FULL, abort_flag);
             if (ok && nblk > 0) ok = issue_qk(0);
             for (int j = 0; ok && j < nblk; ++j) {
-                if (j + 1 < nblk) {
-                    ok = issue_qk(j + 1);
-                    if (!ok) break;
-                }
-                const int s = j & 1;
-                const uint32_t ph = (uint32_t)((j >> 1) & 1);
-                if (!mbar_wait(&v_full[s], ph, p.d_status, KST_WAIT_FULL, abort_flag)) break;
-                if (!mbar_wait(p_full, (uint32_t)(j & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag)) break;
+                if (j + 1 < nblk && !issue_qk(j + 1)) break;
+                const int sv = j % ATT_KV_STAGES;
+                if (!mbar_wait(&v_full[sv], (uint32_t)((j / ATT_KV_STAGES) & 1), p.d_status, KST_WAIT_FULL, abort_flag)) break;
+                if (!mbar_wait(&p_full[t], (uint32_t)(j & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag)) break;
                 tc_fence_after();
-                const uint32_t v_addr = smem_u32(sKV + (2 * s + 1) * ATT_TILE_BYTES);
+                const uint32_t v_addr = smem_u32(tile_ptr(ATT_T_V + sv));
+                // The second 64-column slab of this B operand is the ones tile: its distance from
+                // the V stage is the descriptor's leading byte offset.
+                const uint64_t vdesc0 = make_smem_desc(ones_addr - v_addr, 1024);
 #pragma unroll
                 for (int k = 0; k < ATT_BC / 16; ++k) {
                     // P: 64-key halves are whole tiles apart, 16 keys = 32 B inside a row.
@@ -190,143 +248,182 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                     umma_ss(o_tmem, smem_desc_at(kdesc0, pa), smem_desc_at(vdesc0, v_addr + k * 2048), idesc_o,
                             (j | k) != 0);
                 }
-                umma_commit(&v_empty[s]);
-                umma_commit(pv_done);
+                umma_commit(&pv_done[t]);
+                umma_commit(&v_empty[sv]);   // one of `ntiles` arrivals that free this V stage
             }
         }
     } else {
         // ------------------------------------------------------- softmax + epilogue
-        const int quad = warp & 3;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        const int t = warp >> 2;               // which query tile this warpgroup owns
+        const int quad = warp & 3;             // TMEM lane quadrant
         const int row = quad * 32 + lane;
-        const uint32_t lane_base = uint32_t(quad * 32) << 16;
-        const uint32_t s_tmem = tmem_base + lane_base + ATT_S_COL;
-        const uint32_t o_tmem = tmem_base + lane_base + ATT_O_COL;
-        const float sc = p.scale_log2;
-        float m_run = -INFINITY, l_run = 0.f;
-        uint8_t* prow = sP + row * 128;
-        bool ok = true;
+        if (t < ntiles) {
+            const uint32_t lane_base = uint32_t(quad * 32) << 16;
+            const uint32_t s_tmem = tmem_base + lane_base + ATT_S_COL + t * 128;
+            const uint32_t o_tmem = tmem_base + lane_base + ATT_O_COL + t * 128;
+            const float sc = p.scale_log2;
+            float m_run = -INFINITY;
+            uint8_t* prow = tile_ptr(ATT_T_P + 2 * t) + row * 128;
+            bool ok = true;
+            // Both tiles take the same time per block, and left alone they fall into step: both
+            // want the MUFU pipe in the same half of every period and leave it idle in the other.
+            // So the exponential phases take turns (tile 0 block j, tile 1 block j, tile 0 block
+            // j+1, ...): while one tile owns the MUFU pipe the other does its max / rescale / waits
+            // and its tensor-core work runs.
+            const bool pingpong = ntiles == 2;
 
-        for (int j = 0; j < nblk; ++j) {
-            if (!mbar_wait(s_full, (uint32_t)(j & 1), p.d_status, KST_WAIT_TMEM_FULL, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            const int kv0 = j * ATT_BC;
-            const int nvalid = p.Lk - kv0; // keys of this block that exist (>= 128 when full)
 
-            // Pass 1: the row maximum of the scaled scores.
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(s_tmem + c * 32, r);
+            for (int j = 0; ok && j < nblk; ++j) {
+                if (!mbar_wait(&s_full[t], (uint32_t)(j & 1), p.d_status, KST_WAIT_TMEM_FULL, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const int nvalid = p.Lk - j * ATT_BC; // keys of this block that exist (>= 128 when full)
+                if (lane == 0 && quad == 0 && j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 2);  // S(0, j) ready
+
+                // The whole row of S (128 fp32) comes into registers in one round trip; S is then
+                // free for the next Q K' of this tile.
+                uint32_t r[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, r[c]);
                 tmem_wait_ld();
-                if (nvalid >= ATT_BC) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_empty[t]);
+                if (lane == 0 && quad == 0 && j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 3);  // S in registers
+
+                // Row maximum of the raw scores (the scale is positive, so it commutes with max);
+                // eight independent chains instead of one 128-long dependent one.
+                if (nvalid < ATT_BC) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]) * sc);
-                } else {
+                    for (int c = 0; c < 4; ++c)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (c * 32 + i < nvalid) mx = fmaxf(mx, __uint_as_float(r[i]) * sc);
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i >= nvalid) r[c][i] = 0xff800000u; // -inf: a key that does not exist gives 2^-inf = 0
                 }
-            }
-            const float m_new = fmaxf(m_run, mx);
-            const float alpha = ex2(m_run - m_new); // 0 on the first block (m_run = -inf)
+                float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        mxa = fmaxf(mxa, __uint_as_float(r[c][i]));
+                        mxb = fmaxf(mxb, __uint_as_float(r[c][i + 1]));
+                        mxc = fmaxf(mxc, __uint_as_float(r[c][i + 2]));
+                        mxd = fmaxf(mxd, __uint_as_float(r[c][i + 3]));
+                    }
+                }
+                const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+                // The reference point of the exponentials only has to keep 2^(x - m) inside fp16:
+                // it follows the true maximum lazily, moving (and rescaling O and the running sum)
+                // only when the maximum has grown by more than 2^8.  Any reference point gives the
+                // same quotient O / l; the lazy one makes rescales rare after the first blocks.
+                const float m_blk = mx * sc;
+                const float m_new = (m_blk > m_run + 8.0f) ? m_blk : m_run;
+                const float alpha = ex2(m_run - m_new); // 0 on the first block (m_run = -inf), else 1 or < 2^-8
 
-            // P's shared tile and O are both still in use by the previous block's P V.
-            if (j > 0 && !mbar_wait(pv_done, (uint32_t)((j - 1) & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag)) {
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-
-            // Pass 2: exponentials, row sum, P as fp16 into the swizzled K-major tile.
-            float rs = 0.f;
+                // P's shared tile and O are both still in use by the previous block's P V.
+                if (j > 0 && !mbar_wait(&pv_done[t], (uint32_t)((j - 1) & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                if (lane == 0 && quad == 0 && j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 4);  // max done, PV(j-1) done
+                // Rescale O (and the running sum in its column 64) when this row's maximum moved;
+                // skipped warp-wide when no row's did — exact, the factor would be 1.
+                if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(s_tmem + c * 32, r);
-                tmem_wait_ld();
-                float e[32];
+                    for (int c = 0; c < ATT_ON / 16; ++c) {   // 16 columns at a time: S is live in registers
+                        uint32_t o16[16];
+                        tmem_ld16(o_tmem + c * 16, o16);
+                        tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float v = ex2(fmaf(__uint_as_float(r[i]), sc, -m_new));
-                    if (nvalid < ATT_BC && c * 32 + i >= nvalid) v = 0.f;
-                    e[i] = v;
-                    rs += v;
+                        for (int i = 0; i < 16; ++i) o16[i] = __float_as_uint(__uint_as_float(o16[i]) * alpha);
+                        tmem_st16_raw(o_tmem + c * 16, o16);
+                    }
+                    tmem_wait_st();
                 }
-                uint8_t* half_tile = prow + (c >> 1) * ATT_TILE_BYTES;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint4 o;
-                    __half2* hh = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) hh[t] = __floats2half2_rn(e[q * 8 + 2 * t], e[q * 8 + 2 * t + 1]);
-                    const int chunk = (c & 1) * 4 + q;
-                    *reinterpret_cast<uint4*>(half_tile + ((chunk ^ (row & 7)) << 4)) = o;
-                }
-            }
-            // S has been read out: the next Q K' may overwrite it.
-            tc_fence_before();
-            mbar_arrive(s_empty);
 
-            // Rescale O when this row's maximum moved (skipped warp-wide when none did).
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+                if (pingpong && (t == 1 || j > 0)) {
+                    // tile 0 waits for tile 1's block j-1, tile 1 for tile 0's block j
+                    const uint32_t par = (uint32_t)((t == 1 ? j : j - 1) & 1);
+                    if (!mbar_wait(&exp_turn[t], par, p.d_status, KST_WAIT_SOFTMAX, abort_flag)) { ok = false; break; }
+                }
+                if (lane == 0 && quad == 0 && j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 5);  // rescale done, my turn
+                // P = 2^(s*scale - m) as fp16, two per MUFU op, into the swizzled K-major tile.
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float x0 = fmaf(__uint_as_float(r[c][2 * i]), sc, -m_new);
+                        const float x1 = fmaf(__uint_as_float(r[c][2 * i + 1]), sc, -m_new);
+                        pk[i] = ex2_pack_f16x2(x0, x1);
+                    }
+                    uint8_t* half_tile = prow + (c >> 1) * ATT_TILE_BYTES;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int chunk = (c & 1) * 4 + q;
+                        *reinterpret_cast<uint4*>(half_tile + ((chunk ^ (row & 7)) << 4)) =
+                            make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+                    }
+                    // Hand the turn over half way: the other tile's exponentials then overlap the
+                    // second half of these, which keeps the MUFU pipe fed without falling in step.
+                    if (c == ATT_TURN_AT && pingpong) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&exp_turn[1 - t]);
+                    }
+                }
+                m_run = m_new;
+                fence_proxy_async_smem();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[t]);
+                if (lane == 0 && quad == 0 && j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 6);  // P written
+                if (lane == 0 && j == 3) ATT_TRACE(56 + 64 * t + quad);                  // per-warp P written, block 3
+            }
+
+            // Epilogue: O / l to global through the caller's output strides.
+            if (ok && nblk > 0)
+                ok = mbar_wait(&pv_done[t], (uint32_t)((nblk - 1) & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag);
+            if (ok) {
+                tc_fence_after();
+                const int lq = q0 + t * ATT_BR + row;
+                float inv = 1.0f;
+                {
+                    uint32_t r16[16];
+                    tmem_ld16(o_tmem + 64, r16);
+                    tmem_wait_ld();
+                    const float l = __uint_as_float(r16[0]);
+                    inv = 1.0f / (l == 0.f ? 1.0f : l);
+                }
+                const int64_t obase = lq * p.osL + h * p.osH + b * p.osB;
 #pragma unroll 1
                 for (int c = 0; c < ATT_EP / 32; ++c) {
                     uint32_t r[32];
                     tmem_ld32(o_tmem + c * 32, r);
                     tmem_wait_ld();
+                    if (lq < p.Lq) {
+                        if (p.out_f32) {
+                            float* o = static_cast<float*>(p.out) + obase + c * 32;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    tmem_st32(o_tmem + c * 32, r);
-                }
-                tmem_wait_st();
-            }
-            l_run = l_run * alpha + rs;
-            m_run = m_new;
-            fence_proxy_async_smem();
-            tc_fence_before();
-            mbar_arrive(p_full);
-        }
-
-        // Epilogue: O / l to global, dense (E, Lq, H, B).
-        if (ok && nblk > 0) ok = mbar_wait(pv_done, (uint32_t)((nblk - 1) & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag);
-        if (ok) {
-            tc_fence_after();
-            const float inv = 1.0f / (l_run == 0.f ? 1.0f : l_run);
-            const int lq = q0 + row;
-            const int64_t obase = lq * p.osL + h * p.osH + b * p.osB;
-#pragma unroll 1
-            for (int c = 0; c < ATT_EP / 32; ++c) {
-                uint32_t r[32];
-                if (nblk > 0) {
-                    tmem_ld32(o_tmem + c * 32, r);
-                    tmem_wait_ld();
-                } else {
+                            for (int i = 0; i < 32; i += 4) {
+                                if (c * 32 + i < p.E)
+                                    *reinterpret_cast<float4*>(o + i) =
+                                        make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
+                                                    __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                            }
+                        } else {
+                            __half* o = static_cast<__half*>(p.out) + obase + c * 32;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = 0u;
-                }
-                if (lq < p.Lq) {
-                    if (p.out_f32) {
-                        float* o = static_cast<float*>(p.out) + obase + c * 32;
+                            for (int i = 0; i < 32; i += 8) {
+                                if (c * 32 + i < p.E) {
+                                    uint4 w;
+                                    __half2* hh = reinterpret_cast<__half2*>(&w);
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            if (c * 32 + i < p.E)
-                                *reinterpret_cast<float4*>(o + i) =
-                                    make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
-                                                __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-                        }
-                    } else {
-                        __half* o = static_cast<__half*>(p.out) + obase + c * 32;
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            if (c * 32 + i < p.E) {
-                                uint4 w;
-                                __half2* hh = reinterpret_cast<__half2*>(&w);
-#pragma unroll
-                                for (int t = 0; t < 4; ++t)
-                                    hh[t] = __floats2half2_rn(__uint_as_float(r[i + 2 * t]) * inv,
-                                                              __uint_as_float(r[i + 2 * t + 1]) * inv);
-                                *reinterpret_cast<uint4*>(o + i) = w;
+                                    for (int u = 0; u < 4; ++u)
+                                        hh[u] = __floats2half2_rn(__uint_as_float(r[i + 2 * u]) * inv,
+                                                                  __uint_as_float(r[i + 2 * u + 1]) * inv);
+                                    *reinterpret_cast<uint4*>(o + i) = w;
+                                }
                             }
                         }
                     }
@@ -340,7 +437,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem_base, ATT_TMEM_COLS);
     }
@@ -484,7 +581,7 @@ int b200_attention_f16_strided(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk,
     B200_REQUIRE(k->ptr && v->ptr, B200_EINVAL, "attention: null array");
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     const bool tc = tc_reason(E, Lq, Lk, H, B, q->stride, k->stride, v->stride) == B200_OK && al16(q->ptr) &&
-                    al16(k->ptr) && al16(v->ptr) && al16(out) && oaligned;
+                    al16(k->ptr) && al16(v->ptr) && al16(out) && oaligned && scale > 0.f;
     if (!tc) {
         B200_REQUIRE(E <= 1024, B200_DECLINE_EXTENT, "attention: E = %lld", (long long)E);
         const int wpb = 4;
@@ -516,7 +613,8 @@ int b200_attention_f16_strided(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk,
     p.osL = o->stride[1]; p.osH = o->stride[2]; p.osB = o->stride[3];
     p.out_f32 = out_dtype == B200_F32;
     p.d_status = ctx->d_status;
-    dim3 grid((unsigned)cdiv(Lq, ATT_BR), (unsigned)H, (unsigned)B);
+    p.trace = ctx->gemm_trace;
+    dim3 grid((unsigned)cdiv(Lq, 2 * ATT_BR), (unsigned)H, (unsigned)B);
     attention_f16_tc_kernel<<<grid, ATT_THREADS, ATT_SMEM_BYTES, ctx->stream>>>(tq, tk, tv, p);
     ctx->launches++;
     B200_CUDA(cudaGetLastError());

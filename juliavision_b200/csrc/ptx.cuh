@@ -26,6 +26,7 @@ enum : int {
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // 2 s
 
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -92,6 +93,42 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* d
         if ((++spins & 63u) == 0) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                atomicCAS(d_status, 0, code);
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// Same contract as mbar_wait, but polling with test_wait instead of the suspending try_wait: a
+// thread parked inside try_wait was seen to resume several hundred nanoseconds after the phase
+// completed, which a latency-critical hand-off (softmax <-> UMMA) cannot afford.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, int* d_status, int code,
+                                               volatile int* abort_flag) {
+    if (mbar_test_wait(bar, parity)) return true;
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((++spins & 1023u) == 0) {
+            if (*abort_flag) return false;
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > WAIT_LIMIT_NS) {
                 atomicCAS(d_status, 0, code);
                 *abort_flag = 1;
                 return false;
