@@ -123,6 +123,7 @@ def kernel_figures(ctx, jv, pk, quick: bool):
         def go():
             X, Wt, b, o = sets[i[0] % nbuf]
             i[0] += 1
+            ctx.ws.reset()   # each call is one op: its scratch (stream-K partials) is reused by the next
             jv.matmul_(ctx, o, Wt, X, b, epi=epi)
 
         for _ in range(3):
@@ -302,6 +303,7 @@ def main():
         ff = enc._buf("f", np.float16, f, L)
         qkv = enc._buf("qkv", np.float16, 3 * d, L)
         for w in enc.layers:
+            ctx.ws.reset()
             jv.matmul_(ctx, qkv, w["wqkv"], h, w["bqkv"])
             jv.matmul_(ctx, h, w["wo"], att_t, w["bo"])
             jv.matmul_(ctx, ff, w["w1"], h, w["b1"], epi="gelu")

@@ -159,6 +159,9 @@ int b200_ctx_create(int device, b200_ctx** out) {
     e = cudaMalloc(&c->d_status, 256);
     if (e != cudaSuccess) { cudaStreamDestroy(c->stream); delete c; return fail_cuda(e, "cudaMalloc(status)"); }
     cudaMemset(c->d_status, 0, 256);
+    e = cudaMalloc(&c->sk_flags, SK_FLAG_COUNT * sizeof(int));
+    if (e != cudaSuccess) { cudaFree(c->d_status); cudaStreamDestroy(c->stream); delete c; return fail_cuda(e, "cudaMalloc(flags)"); }
+    cudaMemset(c->sk_flags, 0, SK_FLAG_COUNT * sizeof(int));
     cudaEventCreate(&c->ev0);
     cudaEventCreate(&c->ev1);
     void* fn = nullptr;
@@ -180,6 +183,7 @@ int b200_ctx_destroy(b200_ctx* c) {
     for (auto& kv : c->free_blocks) cudaFree(kv.second);
     for (auto& kv : c->live_blocks) cudaFree(kv.first);
     if (c->d_status) cudaFree(c->d_status);
+    if (c->sk_flags) cudaFree(c->sk_flags);
     if (c->ev0) cudaEventDestroy(c->ev0);
     if (c->ev1) cudaEventDestroy(c->ev1);
     if (c->stream) cudaStreamDestroy(c->stream);

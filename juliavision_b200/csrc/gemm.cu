@@ -65,6 +65,9 @@ template <typename OutT> struct GemmParams {
     const __half* bias;
     int bias_per_n;        // 0: bias[i] over features (M); 1: bias[j] over tokens (N)
     int epilogue;
+    int streamk;           // 0: whole tiles, strided over the workers; 1: equal k-block ranges per worker
+    float* sk_part;        // stream-K: fp32 partial accumulators, one 128 x BN block per (worker, CTA rank)
+    int* sk_flag;          // stream-K: one flag per (worker, CTA rank, epilogue warp), zero between launches
     int* d_status;
     unsigned long long* trace;  // optional timeline of worker 0 (globaltimer ns), null in normal use
 };
@@ -107,6 +110,61 @@ __device__ __forceinline__ float apply_act(int epi, float v) {
         }
         default: return v;
     }
+}
+
+// The work of one worker (a CTA, or a CTA pair) as a sequence of segments, a segment being the
+// k-blocks [kb0, kb1) of one tile.
+//   whole-tile mode: worker w takes tiles w, w + W, w + 2W, ... each with all its k-blocks;
+//   stream-K mode:   the (tile, k-block) pairs, tile-major, are cut into W equal contiguous ranges,
+//                    so every worker does the same number of k-blocks whatever the tile count.  A
+//                    tile cut by a range boundary is finished by the worker that holds its first
+//                    k-block (that segment comes last in the worker's range); the workers holding
+//                    its later k-blocks (their first segment) leave fp32 partials for it.
+struct SegIter {
+    int64_t tile, u, uend, step, total_tiles;
+    int kb0, kb1, nkb, streamk;
+    __device__ __forceinline__ static int64_t range_start(int64_t units, int64_t w, int64_t W) { return units * w / W; }
+    __device__ __forceinline__ void set() {
+        if (streamk) {
+            tile = u / nkb;
+            kb0 = (int)(u - tile * nkb);
+            const int64_t left = uend - u;
+            kb1 = (int)((int64_t)(nkb - kb0) < left ? nkb : kb0 + left);
+        } else {
+            tile = u;
+            kb0 = 0;
+            kb1 = nkb;
+        }
+    }
+    __device__ __forceinline__ void init(int64_t total_tiles_, int nkb_, int streamk_, int64_t w, int64_t W) {
+        total_tiles = total_tiles_;
+        nkb = nkb_;
+        streamk = streamk_;
+        if (streamk) {
+            u = range_start(total_tiles * nkb, w, W);
+            uend = range_start(total_tiles * nkb, w + 1, W);
+            step = 0;
+        } else {
+            u = w;
+            uend = total_tiles;
+            step = W;
+        }
+        set();
+    }
+    __device__ __forceinline__ bool valid() const { return u < uend; }
+    __device__ __forceinline__ void next() {
+        u += streamk ? (int64_t)(kb1 - kb0) : step;
+        set();
+    }
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 template <int BN, typename OutT, int NCTA>
@@ -179,12 +237,14 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int64_t tile = worker; ok && tile < p.total_tiles; tile += nworkers) {
+            SegIter seg;
+            for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); ok && seg.valid(); seg.next()) {
+                const int64_t tile = seg.tile;
                 const int batch = (int)(tile / tiles_per_batch);
                 const int rem = (int)(tile % tiles_per_batch);
                 const int m0 = (rem % p.tiles_m) * BN + (int)rank * Cfg::B_COLS;
                 const int n0 = (rem / p.tiles_m) * TILE_N + (int)rank * GEMM_BM;
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
                     if (!mbar_wait(&empty[s], ph ^ 1, p.d_status, KST_WAIT_EMPTY, abort_flag)) {
                         ok = false;
                         break;
@@ -222,7 +282,8 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             uint32_t ph = 0;
             bool ok = true;
             int64_t it = 0;
-            for (int64_t tile = worker; ok && tile < p.total_tiles; tile += nworkers, ++it) {
+            SegIter seg;
+            for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); ok && seg.valid(); seg.next(), ++it) {
                 const int acc = (int)(it & 1);
                 const uint32_t aph = (uint32_t)((it >> 1) & 1);
                 if constexpr (NCTA == 2) {
@@ -232,7 +293,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
                     bool got;
                     if constexpr (NCTA == 2) got = mbar_wait_cluster(&full[s], ph, p.d_status, KST_WAIT_FULL, abort_flag);
                     else got = mbar_wait(&full[s], ph, p.d_status, KST_WAIT_FULL, abort_flag);
@@ -241,7 +302,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         break;
                     }
                     tc_fence_after();
-                    if (kb == 0 && it == 0) GEMM_TRACE(3); // first stage landed
+                    if (kb == seg.kb0 && it == 0) GEMM_TRACE(3); // first stage landed
                     const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
                     const uint32_t b_addr = a_addr + Cfg::A_BYTES;
 #pragma unroll
@@ -250,8 +311,9 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         // MN-major B: +16 k-rows = two 8-row groups = +2048 B.
                         const uint64_t ad = smem_desc_at(adesc0, a_addr + k * 32);
                         const uint64_t bd = smem_desc_at(bdesc0, b_addr + k * 2048);
-                        if constexpr (NCTA == 2) umma_ss_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
-                        else umma_ss(d_tmem, ad, bd, idesc, (kb | k) != 0);
+                        const uint32_t accum = (kb != seg.kb0 || k != 0); // a segment starts a fresh accumulator
+                        if constexpr (NCTA == 2) umma_ss_pair(d_tmem, ad, bd, idesc, accum);
+                        else umma_ss(d_tmem, ad, bd, idesc, accum);
                     }
                     if constexpr (NCTA == 2) umma_commit_pair(&empty[s], 3); // frees the stage in both CTAs
                     else umma_commit(&empty[s]);
@@ -279,19 +341,68 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         uint8_t* wstg = reinterpret_cast<uint8_t*>(sbias + EPI_WARPS * BN) + ew * 2048;
         __half* wbias = sbias + ew * BN;
         int64_t it = 0;
-        for (int64_t tile = worker; tile < p.total_tiles; tile += nworkers, ++it) {
+        SegIter seg;
+        for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); seg.valid(); seg.next(), ++it) {
+            const int64_t tile = seg.tile;
             const int batch = (int)(tile / tiles_per_batch);
             const int rem = (int)(tile % tiles_per_batch);
             const int m0 = (rem % p.tiles_m) * BN;
             const int n0 = (rem / p.tiles_m) * TILE_N + (int)rank * GEMM_BM;
             const int acc = (int)(it & 1);
             const uint32_t aph = (uint32_t)((it >> 1) & 1);
+            // Stream-K roles of this segment: a contributor holds later k-blocks of a tile some other
+            // worker finishes; a finisher holds the tile's first k-block and collects what the
+            // following workers left for it.
+            const bool contributor = seg.kb0 > 0;
+            int ncontrib = 0;
+            if (!contributor && seg.kb1 < seg.nkb) {
+                const int64_t units = p.total_tiles * seg.nkb, tile_end = (tile + 1) * seg.nkb;
+                while (worker + 1 + ncontrib < nworkers &&
+                       SegIter::range_start(units, worker + 1 + ncontrib, nworkers) < tile_end)
+                    ++ncontrib;
+            }
+            constexpr int PART_PER_WARP = (BN / 2) * 32;                 // floats one epilogue warp owns of a tile
+            const int64_t my_slot = ((int64_t)worker * NCTA + rank) * EPI_WARPS + ew;
+            bool sk_ok = true;
+            if (ncontrib > 0) {
+                // Wait (bounded) for the matching warp of every contributor; they wrote these at the
+                // very start of their ranges, this segment is the last of ours.
+                for (int c = 0; c < ncontrib && sk_ok; ++c) {
+                    const int* f = p.sk_flag + (((int64_t)(worker + 1 + c) * NCTA + rank) * EPI_WARPS + ew);
+                    unsigned long long t0 = 0;
+                    uint32_t spins = 0;
+                    while (ld_acquire_gpu(f) == 0) {
+                        if ((++spins & 255u) == 0) {
+                            const unsigned long long now = globaltimer_ns();
+                            if (t0 == 0) t0 = now;
+                            if (*abort_flag || now - t0 > WAIT_LIMIT_NS) {
+                                atomicCAS(p.d_status, 0, KST_WAIT_STREAMK);
+                                *abort_flag = 1;
+                                sk_ok = false;
+                                break;
+                            }
+                        }
+                    }
+                }
+                sk_ok = !__any_sync(0xffffffffu, !sk_ok);
+            }
+
+            // The first contributor's slab is fetched one slab ahead of its use, so the L2 round trip
+            // runs under the previous slab's conversion and stores.
+            float4 pf[SUB / 4];
+            auto fetch_part = [&](int c, int i) {
+                const int64_t slot = ((int64_t)(worker + 1 + c) * NCTA + rank) * EPI_WARPS + ew;
+                const float4* src = reinterpret_cast<const float4*>(p.sk_part + slot * PART_PER_WARP + (size_t)i * (SUB * 32));
+#pragma unroll
+                for (int q = 0; q < SUB / 4; ++q) pf[q] = __ldcg(src + q * 32 + lane);
+            };
+            if (ncontrib > 0 && sk_ok) fetch_part(0, 0);
 
             __syncwarp(); // the previous tile's readers of wbias are done
             for (int j = lane; j < BN; j += 32)
                 wbias[j] = (p.bias != nullptr && !p.bias_per_n && m0 + j < p.M) ? p.bias[m0 + j] : __float2half(0.f);
-            const float rbias =
-                (p.bias != nullptr && p.bias_per_n && n0 + row < p.N) ? __half2float(p.bias[n0 + row]) : 0.f;
+            const float rbias = (!contributor && p.bias != nullptr && p.bias_per_n && n0 + row < p.N)
+                                    ? __half2float(p.bias[n0 + row]) : 0.f;   // the finisher adds the bias
             const bool got = mbar_wait(&tfull[acc], aph, p.d_status, KST_WAIT_TMEM_FULL, abort_flag);
             if (__any_sync(0xffffffffu, !got)) break; // one answer per warp
             tc_fence_after();
@@ -320,6 +431,26 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         for (int t = 0; t < 16; ++t) v[t] = __uint_as_float(r[t]) + rbias;
                     }
                 }
+                if (contributor) {
+                    // Leave the raw fp32 accumulator slab for the finisher: [quarter q][lane] float4,
+                    // so each store instruction of the warp writes 512 contiguous bytes.
+                    float4* dst = reinterpret_cast<float4*>(p.sk_part + my_slot * PART_PER_WARP + (size_t)i * (SUB * 32));
+#pragma unroll
+                    for (int q = 0; q < SUB / 4; ++q)
+                        dst[q * 32 + lane] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                } else if (ncontrib > 0 && sk_ok) {
+                    for (int c = 0; c < ncontrib; ++c) {
+                        if (c > 0) fetch_part(c, i);
+#pragma unroll
+                        for (int q = 0; q < SUB / 4; ++q) {
+                            v[4 * q] += pf[q].x;
+                            v[4 * q + 1] += pf[q].y;
+                            v[4 * q + 2] += pf[q].z;
+                            v[4 * q + 3] += pf[q].w;
+                        }
+                    }
+                    if (i + 1 < NSLAB) fetch_part(0, i + 1);
+                }
                 if (i == NSLAB - 1) {
                     // This warp has read all it needs of the accumulator: hand it back (leader CTA).
                     tc_fence_before();
@@ -329,7 +460,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         else mbar_arrive(&tempty[acc]);
                     }
                 }
-                if (m0 + col0 >= p.M || rows_valid <= 0) continue; // slab entirely outside the output
+                if (contributor || m0 + col0 >= p.M || rows_valid <= 0) continue; // nothing to write to the output
 
                 // registers -> shared, lane = row; 16-byte piece j of row r sits at piece j ^ ((r>>1)&3)
                 uint8_t* rowp = wstg + lane * 64;
@@ -401,6 +532,16 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                 }
                 __syncwarp(); // the slab is free for the next round
             }
+            if (contributor) {
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) st_release_gpu(p.sk_flag + my_slot, 1);
+            } else if (ncontrib > 0) {
+                __syncwarp();
+                if (lane == 0)   // consumed: the flags are zero again for the next launch
+                    for (int c = 0; c < ncontrib; ++c)
+                        p.sk_flag[((int64_t)(worker + 1 + c) * NCTA + rank) * EPI_WARPS + ew] = 0;
+            }
             if (ew == 0 && lane == 0) GEMM_TRACE(12 + (it < 4 ? it : 3)); // epilogue of tile `it` done
         }
     }
@@ -447,34 +588,61 @@ __global__ void gemm_f16_scalar_kernel(int64_t M, int64_t N, int64_t K, const __
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 struct TilePick {
-    int bn;    // feature columns per tile
-    int ncta;  // 1: 128-token tiles, one CTA each; 2: 256-token tiles, one CTA pair each
+    int bn;      // feature columns per tile
+    int ncta;    // 1: 128-token tiles, one CTA each; 2: 256-token tiles, one CTA pair each
+    int streamk; // 1: equal k-block ranges per worker instead of whole tiles
 };
 
-// Tile planner.  Candidates are (BN, NCTA); the cost of a launch is waves x (per-tile main loop +
-// a fixed per-tile cost), in units of "one CTA pair at full tensor rate".  Single-CTA tiles feed
-// the tensor core from shared memory below its rate (measured ~0.73 at BN=256, less for narrower
-// tiles); pair tiles run it at rate but need twice the tokens to fill a tile.
-static TilePick pick_tile(int64_t M, int64_t N, int64_t nbatch, int sms) {
-    if (const char* f = getenv("B200_GEMM_TILE")) { // debugging aid: "<bn>x<ncta>", e.g. 256x2
+// Tile planner.  Candidates are (BN, NCTA, whole-tile | stream-K); the estimate for each is
+//   whole tiles: waves x (k-blocks x t_kb + t_tile)      stream-K: (tiles x k-blocks / workers) x t_kb + t_tile + t_fix
+// with t_kb the time one worker takes per k-block when the whole GPU is pulling operands through
+// L2 (measured on B200: it is the L2 -> SM traffic per k-block that sets it, ~83 GB/s per SM), t_tile
+// the part of a tile's epilogue nothing hides, and t_fix the stream-K partial hand-off.
+// Workers a stream-K launch uses so that no tile is cut more than once (0: not applicable).
+static int64_t streamk_workers(int64_t tiles, int64_t workers_max) {
+    if (tiles >= workers_max) return workers_max;
+    if (2 * tiles <= workers_max) return 2 * tiles;
+    return 0;
+}
+
+static TilePick pick_tile(int64_t M, int64_t N, int64_t K, int64_t nbatch, int sms) {
+    if (const char* f = getenv("B200_GEMM_TILE")) { // debugging aid: "<bn>x<ncta>[s]", e.g. 256x2 or 256x2s
         int bn = 0, nc = 0;
-        if (sscanf(f, "%dx%d", &bn, &nc) == 2 && (bn == 256 || bn == 128 || (bn == 64 && nc == 1)) && (nc == 1 || nc == 2))
-            return {bn, nc};
+        char sk = 0;
+        const int got = sscanf(f, "%dx%d%c", &bn, &nc, &sk);
+        if (got >= 2 && (bn == 256 || bn == 128 || (bn == 64 && nc == 1)) && (nc == 1 || nc == 2))
+            return {bn, nc, got == 3 && sk == 's'};
     }
-    struct Cand { int bn, ncta; double rate; };
-    const Cand cands[5] = {{256, 2, 1.0}, {128, 2, 0.70}, {256, 1, 0.73}, {128, 1, 0.62}, {64, 1, 0.42}};
-    TilePick best{256, 1};
+    struct Cand { int bn, ncta; double t_kb; };
+    const Cand cands[5] = {{256, 2, 0.39}, {128, 2, 0.38}, {256, 1, 0.50}, {128, 1, 0.38}, {64, 1, 0.32}};
+    const int64_t nkb = cdiv(K, GEMM_BK);
+    const double t_tile = 2.0, t_fix = 8.0;  // measured: partial dump + fence + flag + read-back
+    TilePick best{256, 1, 0};
     double best_cost = 1e300;
+    for (const Cand& c : cands) {   // whole-tile schedules first: stream-K has to beat the best of them clearly
+        const int64_t tiles = cdiv(M, c.bn) * cdiv(N, (int64_t)GEMM_BM * c.ncta) * nbatch;
+        const int64_t waves = cdiv(tiles, (int64_t)(sms / c.ncta));
+        const double dp = (double)waves * ((double)nkb * c.t_kb + t_tile);
+        if (dp < best_cost - 1e-9) {
+            best_cost = dp;
+            best = {c.bn, c.ncta, 0};
+        }
+    }
+    best_cost *= 0.85;
     for (const Cand& c : cands) {
         const int64_t tiles = cdiv(M, c.bn) * cdiv(N, (int64_t)GEMM_BM * c.ncta) * nbatch;
         const int64_t workers = sms / c.ncta;
         const int64_t waves = cdiv(tiles, workers);
-        // work per tile relative to a 256x256 pair tile, divided by the rate it runs at
-        const double tile_work = (double)c.bn * c.ncta / 512.0 / c.rate * (c.ncta == 2 ? 1.0 : 2.0);
-        const double cost = (double)waves * (tile_work + 0.08);
-        if (cost < best_cost - 1e-9) {
-            best_cost = cost;
-            best = {c.bn, c.ncta};
+        // Stream-K pays when the whole-tile schedule leaves a wave mostly empty.  Only splits
+        // that cut a tile at most once are considered (one contributor per finisher keeps the
+        // hand-off short): all workers when there is at least a tile each, else two per tile.
+        const int64_t skw = streamk_workers(tiles, workers);
+        if (skw > 0 && tiles % workers != 0 && waves <= 3 && nkb >= 8) {
+            const double sk = (double)(tiles * nkb) / (double)skw * c.t_kb + t_tile + t_fix;
+            if (sk < best_cost - 1e-9) {
+                best_cost = sk;
+                best = {c.bn, c.ncta, 1};
+            }
         }
     }
     return best;
@@ -483,7 +651,7 @@ static TilePick pick_tile(int64_t M, int64_t N, int64_t nbatch, int sms) {
 template <int BN, typename OutT, int NCTA>
 static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
                      const void* B, int64_t ldb, const void* bias, int bias_per_n, void* out, int64_t ldo,
-                     int epi, int64_t nbatch, int64_t sA, int64_t sB, int64_t sO) {
+                     int epi, int64_t nbatch, int64_t sA, int64_t sB, int64_t sO, int streamk) {
     using Cfg = GemmCfg<BN, OutT, NCTA>;
     static bool attr_done[16] = {};
     auto kern = gemm_f16_tc_kernel<BN, OutT, NCTA>;
@@ -550,7 +718,21 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
         }
         if (resident[ctx->device & 15] < workers_max) workers_max = resident[ctx->device & 15];
     }
-    const int workers = (int)(p.total_tiles < workers_max ? p.total_tiles : workers_max);
+    int workers = (int)(p.total_tiles < workers_max ? p.total_tiles : workers_max);
+    p.streamk = 0;
+    p.sk_part = nullptr;
+    p.sk_flag = ctx->sk_flags;
+    const int64_t skw = streamk_workers(p.total_tiles, workers_max);
+    if (streamk && skw > 0 && p.num_kb >= 2 && ctx->sk_flags != nullptr) {
+        // Every worker gets the same number of k-blocks; partial tiles meet in a workspace block
+        // of one fp32 tile per (worker, CTA rank).
+        workers = (int)skw;
+        void* part = nullptr;
+        int rc = ws_scratch(ctx, (size_t)workers * NCTA * GEMM_BM * BN * sizeof(float), &part);
+        if (rc) return rc;
+        p.streamk = 1;
+        p.sk_part = static_cast<float*>(part);
+    }
     cfg.gridDim = dim3((unsigned)(workers * NCTA), 1, 1);
     B200_CUDA(cudaLaunchKernelEx(&cfg, kern, tX, tW, p));
     ctx->launches++;
@@ -584,7 +766,7 @@ int b200_gemm_f16_plan(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t n
     B200_REQUIRE(ctx && plan, B200_EINVAL, "gemm_plan: null argument");
     B200_REQUIRE(M >= 1 && N >= 1 && K >= 1 && nbatch >= 1, B200_DECLINE_EXTENT, "gemm_plan: empty extent");
     const int sms = ctx->prop.multiProcessorCount;
-    const TilePick t = pick_tile(M, N, nbatch, sms);
+    const TilePick t = pick_tile(M, N, K, nbatch, sms);
     const int bn = t.bn;
     plan->block_m = GEMM_BM * t.ncta;
     plan->block_n = bn;
@@ -654,10 +836,10 @@ int gemm_f16_run(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, 
         B200_CUDA(cudaGetLastError());
         return B200_OK;
     }
-    const TilePick t = pick_tile(M, N, nbatch, ctx->prop.multiProcessorCount);
+    const TilePick t = pick_tile(M, N, K, nbatch, ctx->prop.multiProcessorCount);
 #define GEMM_GO(BN_, T_, NC_)                                                                                     \
     return launch_tc<BN_, T_, NC_>(ctx, M, N, K, A, lda, B, ldb, bias, bias_per_n, out, ldo, epilogue, nbatch, strideA, \
-                                   strideB, strideO)
+                                   strideB, strideO, t.streamk)
     if (out_dtype == B200_F16) {
         if (t.ncta == 2 && t.bn == 256) GEMM_GO(256, __half, 2);
         if (t.ncta == 2) GEMM_GO(128, __half, 2);

@@ -45,6 +45,7 @@ struct b200_ctx {
     cudaStream_t stream = nullptr;
     cudaDeviceProp prop{};
     int* d_status = nullptr;   // device status words: [0] first failed wait code
+    int* sk_flags = nullptr;   // stream-K hand-off flags (zero between launches), SK_FLAG_COUNT ints
     int64_t launches = 0;
     bool capturing = false;
     unsigned long long* gemm_trace = nullptr;  // device buffer of >= 32 slots while tracing, else null
@@ -62,6 +63,8 @@ struct b200_ctx {
     size_t ws_cap = 0, ws_used = 0;
     std::vector<b200::RetiredBlock> ws_retired;
 };
+
+constexpr int SK_FLAG_COUNT = 4096;
 
 struct b200_graph {
     cudaGraphExec_t exec = nullptr;

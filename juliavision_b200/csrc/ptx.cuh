@@ -21,7 +21,8 @@ enum : int {
     KST_WAIT_TMEM_FULL = 103,  // epilogue waited for an accumulator that never completed
     KST_WAIT_TMEM_EMPTY = 104, // MMA issuer waited for an accumulator never drained
     KST_WAIT_SOFTMAX = 105,    // attention: a softmax <-> MMA hand-off never arrived
-    KST_SMEM_LAYOUT = 106      // dynamic shared memory base left no room for the carve-up
+    KST_SMEM_LAYOUT = 106,     // dynamic shared memory base left no room for the carve-up
+    KST_WAIT_STREAMK = 107     // a stream-K finisher waited for a partial tile that never came
 };
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // 2 s
