@@ -164,6 +164,9 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above overlapped the previous kernel's tail; from here on its results are needed.
+    grid_dep_wait();
+    grid_dep_launch();
 
     // Register budget: the two softmax warpgroups hold a full score row per thread; the third
     // warpgroup (one TMA lane, one UMMA lane, two idle warps) needs almost nothing and hands its
@@ -615,9 +618,9 @@ int b200_attention_f16_strided(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk,
     p.d_status = ctx->d_status;
     p.trace = ctx->gemm_trace;
     dim3 grid((unsigned)cdiv(Lq, 2 * ATT_BR), (unsigned)H, (unsigned)B);
-    attention_f16_tc_kernel<<<grid, ATT_THREADS, ATT_SMEM_BYTES, ctx->stream>>>(tq, tk, tv, p);
+    B200_CUDA(launch_dep(attention_f16_tc_kernel, grid, dim3(ATT_THREADS, 1, 1), ATT_SMEM_BYTES, ctx->stream, 1, tq, tk,
+                         tv, p));
     ctx->launches++;
-    B200_CUDA(cudaGetLastError());
     return B200_OK;
 }
 

@@ -2,6 +2,7 @@
 // the tensor-map encoder.  Host-side only; the one kernel here fills memory.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "internal.h"
@@ -20,6 +21,11 @@ int fail(int code, const char* fmt, ...) {
 
 int fail_cuda(cudaError_t e, const char* what) {
     return fail(B200_ECUDA, "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+}
+
+bool pdl_enabled() {
+    static const bool on = getenv("B200_NO_PDL") == nullptr; // debugging aid: plain stream order when set
+    return on;
 }
 
 static size_t round_up(size_t n, size_t a) { return (n + a - 1) / a * a; }

@@ -227,6 +227,9 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
     else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above overlapped the previous kernel's tail; from here on its results are needed.
+    grid_dep_wait();
+    grid_dep_launch();
 
     const int64_t tiles_per_batch = (int64_t)p.tiles_m * p.tiles_n;
     if (threadIdx.x == 0) GEMM_TRACE(1); // setup done
@@ -690,17 +693,6 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
     p.epilogue = epi;
     p.d_status = ctx->d_status;
     p.trace = ctx->gemm_trace;
-    cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-    cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = NCTA;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
     // Persistent workers: as many CTAs (or CTA pairs) as can be resident at once.  Pairs must sit
     // in one GPC, so fewer than SMs/2 may fit; ask the runtime once per device.
     static int resident[16] = {};
@@ -708,6 +700,17 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
     if (NCTA == 2) {
         if (!resident[ctx->device & 15]) {
             int n = 0;
+            cudaLaunchConfig_t cfg = {};
+            cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+            cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+            cfg.stream = ctx->stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = NCTA;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
             cfg.gridDim = dim3((unsigned)(workers_max * NCTA), 1, 1);
             cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
             if (e != cudaSuccess || n <= 0) {
@@ -733,8 +736,8 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
         p.streamk = 1;
         p.sk_part = static_cast<float*>(part);
     }
-    cfg.gridDim = dim3((unsigned)(workers * NCTA), 1, 1);
-    B200_CUDA(cudaLaunchKernelEx(&cfg, kern, tX, tW, p));
+    B200_CUDA(launch_dep(kern, dim3((unsigned)(workers * NCTA), 1, 1), dim3(GEMM_THREADS, 1, 1), Cfg::SMEM_BYTES,
+                         ctx->stream, NCTA, tX, tW, p));
     ctx->launches++;
     return B200_OK;
 }

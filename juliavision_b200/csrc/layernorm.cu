@@ -8,6 +8,7 @@
 #include <cuda_fp16.h>
 
 #include "internal.h"
+#include "ptx.cuh"
 
 namespace b200 {
 
@@ -70,6 +71,8 @@ ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restr
                float* __restrict__ rstd, const InT* __restrict__ gamma,
                const InT* __restrict__ beta, int64_t groups, int C, float eps) {
     constexpr int VN = Vec16<InT>::N;
+    grid_dep_wait();     // the input is the previous kernel's output
+    grid_dep_launch();
     const int lane = threadIdx.x & 31;
     const int64_t g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (g >= groups) return;
@@ -149,6 +152,8 @@ ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half*
                    const __half* __restrict__ beta, int64_t groups, int C, float eps, int use_clamp, float lo,
                    float hi) {
     constexpr int VN = 8;
+    grid_dep_wait();     // x and h are the previous kernels' outputs
+    grid_dep_launch();
     const int lane = threadIdx.x & 31;
     const int64_t g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (g >= groups) return;
@@ -290,9 +295,9 @@ static int launch_ln(b200_ctx* ctx, int64_t groups, int64_t C, const void* a, vo
         const int vpl = (nvec + 31) / 32;
         const int wpb = 4;
         dim3 grid((unsigned)cdiv(groups, wpb)), block(32 * wpb);
-#define LN_GO(V)                                                                                   \
-    ln_warp_kernel<InT, OutT, V><<<grid, block, 0, ctx->stream>>>(ap, op, mean, rstd, gp, bp, groups, \
-                                                                  (int)C, eps)
+#define LN_GO(V)                                                                                            \
+    B200_CUDA(launch_dep(ln_warp_kernel<InT, OutT, V>, grid, block, 0, ctx->stream, 1, ap, op, mean, rstd, gp, bp, \
+                         groups, (int)C, eps))
         if (vpl <= 1) LN_GO(1);
         else if (vpl <= 2) LN_GO(2);
         else if (vpl <= 3) LN_GO(3);
@@ -338,10 +343,10 @@ extern "C" int b200_add_layernorm_f16(b200_ctx* ctx, int64_t groups, int64_t C, 
     }
     const int nvec = (int)(C / 8), vpl = (nvec + 31) / 32, wpb = 4;
     dim3 grid((unsigned)cdiv(groups, wpb)), block(32 * wpb);
-#define LNA_GO(V)                                                                                               \
-    ln_add_warp_kernel<V><<<grid, block, 0, ctx->stream>>>((__half*)x, (const __half*)h, (__half*)out, mean, rstd, \
-                                                            (const __half*)gamma, (const __half*)beta, groups,     \
-                                                            (int)C, eps, use_clamp, lo, hi)
+#define LNA_GO(V)                                                                                                 \
+    B200_CUDA(launch_dep(ln_add_warp_kernel<V>, grid, block, 0, ctx->stream, 1, (__half*)x, (const __half*)h,           \
+                         (__half*)out, mean, rstd, (const __half*)gamma, (const __half*)beta, groups, (int)C, eps, \
+                         use_clamp, lo, hi))
     if (vpl <= 1) LNA_GO(1);
     else if (vpl <= 2) LNA_GO(2);
     else if (vpl <= 3) LNA_GO(3);

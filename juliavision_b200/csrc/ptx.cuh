@@ -50,6 +50,16 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// ----------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while its
+// predecessor in the stream is still running.  grid_dep_wait() blocks until the predecessor has
+// completed and its writes are visible: everything before it (barrier set-up, TMEM allocation,
+// descriptor prefetch) overlaps the predecessor's tail; nothing after it may be hoisted above.
+// grid_dep_launch() lets the successor be scheduled as soon as every CTA of this grid has
+// issued it (or exited).
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ------------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
