@@ -50,13 +50,15 @@ struct AttnParams {
     void* out;
     int64_t osL, osH, osB;  // element strides of out along L, H, B (E is contiguous)
     int out_f32;
+    int qpairs;         // query pairs (256 queries) per (head, batch)
+    int pair_ctas;      // CTAs [0, pair_ctas) own a whole pair; the rest own one tile of a pair each
     int* d_status;
     unsigned long long* trace;  // optional timeline of CTA (0,0,0) (globaltimer ns), null in normal use
 };
 
 #define ATT_TRACE(slot)                                                                              \
     do {                                                                                             \
-        if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 128) \
+        if (p.trace != nullptr && blockIdx.x == 0 && (slot) < 128) \
             p.trace[(slot)] = globaltimer_ns();                                                      \
     } while (0)
 
@@ -118,11 +120,20 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * (2 * ATT_BR);
-    const int h = blockIdx.y;
-    const int b = blockIdx.z;
+    // Work item of this CTA.  Most CTAs own a pair of query tiles; when the pairs do not fill the
+    // last wave of SMs, the pairs of that wave are handed out as single tiles instead (twice as
+    // many, half as long), which shortens the tail.
+    int item = blockIdx.x, half = -1;
+    if (item >= p.pair_ctas) {
+        half = (item - p.pair_ctas) & 1;
+        item = p.pair_ctas + ((item - p.pair_ctas) >> 1);
+    }
+    const int qp = item % p.qpairs;
+    const int h = (item / p.qpairs) % p.H;
+    const int b = item / (p.qpairs * p.H);
+    const int q0 = qp * (2 * ATT_BR) + (half > 0 ? ATT_BR : 0);
     const int nblk = (p.Lk + ATT_BC - 1) / ATT_BC;
-    const int ntiles = (q0 + ATT_BR < p.Lq) ? 2 : 1;   // the second tile may lie wholly past Lq
+    const int ntiles = (half < 0 && q0 + ATT_BR < p.Lq) ? 2 : 1;   // the second tile may lie wholly past Lq
 
     if (threadIdx.x == 0) {
         ATT_TRACE(0);
@@ -617,7 +628,16 @@ int b200_attention_f16_strided(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk,
     p.out_f32 = out_dtype == B200_F32;
     p.d_status = ctx->d_status;
     p.trace = ctx->gemm_trace;
-    dim3 grid((unsigned)cdiv(Lq, 2 * ATT_BR), (unsigned)H, (unsigned)B);
+    p.qpairs = (int)cdiv(Lq, 2 * ATT_BR);
+    const int64_t pairs = (int64_t)p.qpairs * H * B;
+    B200_REQUIRE(pairs < (1ll << 30), B200_DECLINE_EXTENT, "attention: too many query tiles");
+    const int64_t sms = ctx->prop.multiProcessorCount;
+    const int64_t rem = pairs % sms;
+    // Split the pairs of a last wave that would leave more than half of the SMs idle — but not a
+    // pair whose second tile does not exist.
+    int64_t nsplit = (pairs > sms && rem > 0 && 2 * rem <= sms && Lq % (2 * ATT_BR) == 0) ? rem : 0;
+    p.pair_ctas = (int)(pairs - nsplit);
+    dim3 grid((unsigned)(pairs + nsplit), 1, 1);
     B200_CUDA(launch_dep(attention_f16_tc_kernel, grid, dim3(ATT_THREADS, 1, 1), ATT_SMEM_BYTES, ctx->stream, 1, tq, tk,
                          tv, p));
     ctx->launches++;
