@@ -25,24 +25,24 @@ namespace b200 {
 constexpr int ATT_BR = 128;  // queries per tile (TMEM lanes); a CTA owns two tiles
 constexpr int ATT_BC = 128;  // keys per block
 constexpr int ATT_EP = 64;   // head dim padded to one 128-byte swizzle row
-constexpr int ATT_ON = 80;   // P V accumulator columns: 64 of O, then the row sum in column 64
 constexpr int ATT_THREADS = 384;  // warps 0-3, 4-7: softmax of tile 0, 1; warp 8: TMA; warps 9, 10: UMMA; 11 idle
 constexpr int ATT_TILE_BYTES = 128 * 128; // every operand tile is 128 rows x 128 B
-constexpr int ATT_KV_STAGES = 3;
+constexpr int ATT_KV_STAGES = 4;
 #ifndef ATT_TURN_AT
 #define ATT_TURN_AT 1   // after which quarter (0..3) of its exponentials a tile passes the turn
 #endif
 // shared-memory map, in 16 KB tiles
 constexpr int ATT_T_Q = 0;                         // 2 tiles
-constexpr int ATT_T_K = 2;                         // 3 tiles
-constexpr int ATT_T_V = ATT_T_K + ATT_KV_STAGES;   // 3 tiles
-constexpr int ATT_T_ONES = ATT_T_V + ATT_KV_STAGES; // 1 tile: the column of ones that makes P V emit row sums
-constexpr int ATT_T_P = ATT_T_ONES + 1;            // 2 x 2 tiles
-constexpr int ATT_T_END = ATT_T_P + 4;
+constexpr int ATT_T_K = 2;                         // ATT_KV_STAGES tiles
+constexpr int ATT_T_V = ATT_T_K + ATT_KV_STAGES;   // ATT_KV_STAGES tiles
+constexpr int ATT_T_END = ATT_T_V + ATT_KV_STAGES;
 constexpr int ATT_SMEM_BYTES = ATT_T_END * ATT_TILE_BYTES + 256;
+// tensor-memory map (512 columns): S of tile t, fp32, at [128 t, 128 t + 128); O of tile t, fp32, at
+// [256 + 64 t, ... + 64); P of tile t, fp16 packed two keys per column, at [384 + 64 t, ... + 64)
 constexpr int ATT_TMEM_COLS = 512;
-constexpr int ATT_S_COL = 0;    // S of tile t at columns [128 t, 128 t + 128)
-constexpr int ATT_O_COL = 256;  // O of tile t at columns [256 + 128 t, ... + 80)
+constexpr int ATT_S_COL = 0;
+constexpr int ATT_O_COL = 256;
+constexpr int ATT_P_COL = 384;
 
 struct AttnParams {
     int E, Lq, Lk, H, B;
@@ -67,12 +67,6 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// 2^lo, 2^hi as one packed fp16x2 (lo in the low half).  The packed MUFU form
-// (ex2.approx.f16x2) measured slower than two fp32 ex2 plus one pack on this part.
-__device__ __forceinline__ uint32_t ex2_pack_f16x2(float lo, float hi) {
-    __half2 h2 = __floats2half2_rn(ex2(lo), ex2(hi));
-    return *reinterpret_cast<uint32_t*>(&h2);
-}
 __device__ __forceinline__ void tmem_st16_raw(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -86,12 +80,11 @@ __device__ __forceinline__ void tmem_st16_raw(uint32_t taddr, const uint32_t* r)
 //   warps 0-3  softmax of tile 0, warps 4-7 softmax of tile 1: one thread per query row, the whole
 //              128-score row in registers (these two warpgroups take registers from the third)
 //   warp 8     TMA producer: both Q tiles once, then K and V blocks through 3-stage rings
-//   warps 9,10 UMMA issuers, one lane per tile: S_t = Q_t K' and O_t += P_t [V | 1] per key block;
+//   warps 9,10 UMMA issuers, one lane per tile: S_t = Q_t K' and O_t += P_t V per key block;
 //              the two chains are independent, so the tensor core works on one tile while the
 //              other tile's softmax runs
-// The extra "ones" column appended to V makes the tensor core accumulate the softmax denominator
-// (in fp32, from the same fp16-rounded P the numerator uses), so the softmax threads spend their
-// instructions on max / exp only, and exp runs two-wide (ex2.approx.f16x2).
+// P never touches shared memory: the softmax threads write it as packed fp16 into tensor memory and
+// the P V product takes its A operand from there, so the shared-memory port only feeds K and V.
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                         const __grid_constant__ CUtensorMap tmapK,
@@ -105,17 +98,17 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
     }
     auto tile_ptr = [&](int t) { return smem + t * ATT_TILE_BYTES; };
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_T_END * ATT_TILE_BYTES);
-    uint64_t* q_full = bars + 0;    // [2]
-    uint64_t* k_full = bars + 2;    // [3]
-    uint64_t* k_empty = bars + 5;   // [3]
-    uint64_t* v_full = bars + 8;    // [3]
-    uint64_t* v_empty = bars + 11;  // [3]
-    uint64_t* s_full = bars + 14;   // [2]
-    uint64_t* s_empty = bars + 16;  // [2]
-    uint64_t* p_full = bars + 18;   // [2]
-    uint64_t* pv_done = bars + 20;  // [2]
-    uint64_t* exp_turn = bars + 22; // [2]: whose turn it is to run its exponentials
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
+    uint64_t* q_full = bars + 0;                           // [2]
+    uint64_t* k_full = bars + 2;                           // [STAGES]
+    uint64_t* k_empty = k_full + ATT_KV_STAGES;            // [STAGES]
+    uint64_t* v_full = k_empty + ATT_KV_STAGES;            // [STAGES]
+    uint64_t* v_empty = v_full + ATT_KV_STAGES;            // [STAGES]
+    uint64_t* s_full = v_empty + ATT_KV_STAGES;            // [2]
+    uint64_t* s_empty = s_full + 2;                        // [2]
+    uint64_t* p_full = s_empty + 2;                        // [2]
+    uint64_t* pv_done = p_full + 2;                        // [2]
+    uint64_t* exp_turn = pv_done + 2;                      // [2]: whose turn it is to run its exponentials
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(exp_turn + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -161,16 +154,6 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
         tmem_alloc(tmem_slot, ATT_TMEM_COLS);
         tmem_relinquish();
     }
-    if (warp < 4) {
-        // The ones tile, in the MN-major 128-byte-swizzled form of a V tile: key row r is 128 B,
-        // logical 16-byte piece 0 (columns 0..7) sits at physical piece (0 ^ (r & 7)).
-        const int r = warp * 32 + lane;
-        uint4* rowp = reinterpret_cast<uint4*>(tile_ptr(ATT_T_ONES) + r * 128);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) rowp[j] = make_uint4(0u, 0u, 0u, 0u);
-        rowp[r & 7] = make_uint4(0x00003C00u, 0u, 0u, 0u);   // fp16 1.0 in column 0
-        fence_proxy_async_smem();
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -207,23 +190,22 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
         // ------------------------------------------------------------- UMMA issuers
         // One issuing lane per query tile (warp 9: tile 0, warp 10: tile 1).  Each walks its own
         // chain  S_t(j+1) = Q_t K(j+1)'  as soon as the softmax has pulled S_t(j) into registers,
-        // then  O_t += P_t(j) [V(j) | 1]  once P_t(j) is written.  The two chains share only the
+        // then  O_t += P_t(j) V(j)  once P_t(j) is written.  The two chains share only the
         // K/V rings.  (Issuing a UMMA blocks while the tensor pipe is busy, so the issuing lanes
         // are not softmax threads.)
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         const int t = warp - 9;
         if (lane == 0 && t < ntiles) {
-            // S = Q K': both operands K-major (E contiguous).  O += P [V|1]: P K-major (keys
-            // contiguous per query row), V MN-major (E contiguous per key) with the ones tile as
-            // its second 64-column slab.
+            // S = Q K': both operands K-major (E contiguous), from shared memory.  O += P V: P from
+            // tensor memory, V MN-major (E contiguous per key) from shared memory.
             constexpr uint32_t idesc_s = make_idesc_f16(ATT_BR, ATT_BC, 0, 0);
-            constexpr uint32_t idesc_o = make_idesc_f16(ATT_BR, ATT_ON, 0, 1);
+            constexpr uint32_t idesc_o = make_idesc_f16(ATT_BR, ATT_EP, 0, 1);
             constexpr uint64_t kdesc0 = make_smem_desc(16, 1024);
-            const uint32_t ones_addr = smem_u32(tile_ptr(ATT_T_ONES));
+            constexpr uint64_t vdesc0 = make_smem_desc(ATT_TILE_BYTES, 1024);
             const uint32_t q_addr = smem_u32(tile_ptr(ATT_T_Q + t));
-            const uint32_t p_addr = smem_u32(tile_ptr(ATT_T_P + 2 * t));
             const uint32_t s_tmem = tmem_base + ATT_S_COL + t * 128;
-            const uint32_t o_tmem = tmem_base + ATT_O_COL + t * 128;
+            const uint32_t o_tmem = tmem_base + ATT_O_COL + t * 64;
+            const uint32_t p_tmem = tmem_base + ATT_P_COL + t * 64;
 
             auto issue_qk = [&](int j) -> bool {
                 const int sk = j % ATT_KV_STAGES;
@@ -251,16 +233,11 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 if (!mbar_wait(&p_full[t], (uint32_t)(j & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag)) break;
                 tc_fence_after();
                 const uint32_t v_addr = smem_u32(tile_ptr(ATT_T_V + sv));
-                // The second 64-column slab of this B operand is the ones tile: its distance from
-                // the V stage is the descriptor's leading byte offset.
-                const uint64_t vdesc0 = make_smem_desc(ones_addr - v_addr, 1024);
 #pragma unroll
                 for (int k = 0; k < ATT_BC / 16; ++k) {
-                    // P: 64-key halves are whole tiles apart, 16 keys = 32 B inside a row.
+                    // P comes from tensor memory: 16 keys = 8 packed columns per step.
                     // V: 16 key rows = two 8-row groups = 2048 B.
-                    const uint32_t pa = p_addr + (k >> 2) * ATT_TILE_BYTES + (k & 3) * 32;
-                    umma_ss(o_tmem, smem_desc_at(kdesc0, pa), smem_desc_at(vdesc0, v_addr + k * 2048), idesc_o,
-                            (j | k) != 0);
+                    umma_ts(o_tmem, p_tmem + k * 8, smem_desc_at(vdesc0, v_addr + k * 2048), idesc_o, (j | k) != 0);
                 }
                 umma_commit(&pv_done[t]);
                 umma_commit(&v_empty[sv]);   // one of `ntiles` arrivals that free this V stage
@@ -275,10 +252,10 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
         if (t < ntiles) {
             const uint32_t lane_base = uint32_t(quad * 32) << 16;
             const uint32_t s_tmem = tmem_base + lane_base + ATT_S_COL + t * 128;
-            const uint32_t o_tmem = tmem_base + lane_base + ATT_O_COL + t * 128;
+            const uint32_t o_tmem = tmem_base + lane_base + ATT_O_COL + t * 64;
+            const uint32_t p_tmem = tmem_base + lane_base + ATT_P_COL + t * 64;
             const float sc = p.scale_log2;
-            float m_run = -INFINITY;
-            uint8_t* prow = tile_ptr(ATT_T_P + 2 * t) + row * 128;
+            float m_run = -INFINITY, l_run = 0.f;
             bool ok = true;
             // Both tiles take the same time per block, and left alone they fall into step: both
             // want the MUFU pipe in the same half of every period and leave it idle in the other.
@@ -345,7 +322,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 // skipped warp-wide when no row's did — exact, the factor would be 1.
                 if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
-                    for (int c = 0; c < ATT_ON / 16; ++c) {   // 16 columns at a time: S is live in registers
+                    for (int c = 0; c < ATT_EP / 16; ++c) {   // 16 columns at a time: S is live in registers
                         uint32_t o16[16];
                         tmem_ld16(o_tmem + c * 16, o16);
                         tmem_wait_ld();
@@ -362,32 +339,32 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                     if (!mbar_wait(&exp_turn[t], par, p.d_status, KST_WAIT_SOFTMAX, abort_flag)) { ok = false; break; }
                 }
                 if (lane == 0 && quad == 0 && j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 5);  // rescale done, my turn
-                // P = 2^(s*scale - m) as fp16, two per MUFU op, into the swizzled K-major tile.
+                // P = 2^(s*scale - m): fp32 exponentials, their fp32 row sum, and P rounded to fp16
+                // (two keys per 32-bit column) straight into tensor memory for the P V product.
+                float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float x0 = fmaf(__uint_as_float(r[c][2 * i]), sc, -m_new);
-                        const float x1 = fmaf(__uint_as_float(r[c][2 * i + 1]), sc, -m_new);
-                        pk[i] = ex2_pack_f16x2(x0, x1);
+                        const float e0 = ex2(fmaf(__uint_as_float(r[c][2 * i]), sc, -m_new));
+                        const float e1 = ex2(fmaf(__uint_as_float(r[c][2 * i + 1]), sc, -m_new));
+                        ls0 += e0;
+                        ls1 += e1;
+                        const __half2 h2 = __floats2half2_rn(e0, e1);
+                        pk[i] = *reinterpret_cast<const uint32_t*>(&h2);
                     }
-                    uint8_t* half_tile = prow + (c >> 1) * ATT_TILE_BYTES;
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int chunk = (c & 1) * 4 + q;
-                        *reinterpret_cast<uint4*>(half_tile + ((chunk ^ (row & 7)) << 4)) =
-                            make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-                    }
-                    // Hand the turn over half way: the other tile's exponentials then overlap the
-                    // second half of these, which keeps the MUFU pipe fed without falling in step.
+                    tmem_st16_raw(p_tmem + c * 16, pk);
+                    // Hand the turn over part way: the other tile's exponentials then overlap the
+                    // rest of these, which keeps the MUFU pipe fed without falling in step.
                     if (c == ATT_TURN_AT && pingpong) {
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&exp_turn[1 - t]);
                     }
                 }
+                tmem_wait_st();
+                l_run = l_run * alpha + (ls0 + ls1);
                 m_run = m_new;
-                fence_proxy_async_smem();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_full[t]);
@@ -401,14 +378,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
             if (ok) {
                 tc_fence_after();
                 const int lq = q0 + t * ATT_BR + row;
-                float inv = 1.0f;
-                {
-                    uint32_t r16[16];
-                    tmem_ld16(o_tmem + 64, r16);
-                    tmem_wait_ld();
-                    const float l = __uint_as_float(r16[0]);
-                    inv = 1.0f / (l == 0.f ? 1.0f : l);
-                }
+                const float inv = 1.0f / (l_run == 0.f ? 1.0f : l_run);
                 const int64_t obase = lq * p.osL + h * p.osH + b * p.osB;
 #pragma unroll 1
                 for (int c = 0; c < ATT_EP / 32; ++c) {
