@@ -262,7 +262,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
             // So the exponential phases take turns (tile 0 block j, tile 1 block j, tile 0 block
             // j+1, ...): while one tile owns the MUFU pipe the other does its max / rescale / waits
             // and its tensor-core work runs.
-            const bool pingpong = ntiles == 2;
+            const bool pingpong = ntiles == 2 && ATT_TURN_AT >= 0;
 
 
             for (int j = 0; ok && j < nblk; ++j) {
@@ -347,8 +347,9 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float e0 = ex2(fmaf(__uint_as_float(r[c][2 * i]), sc, -m_new));
-                        const float e1 = ex2(fmaf(__uint_as_float(r[c][2 * i + 1]), sc, -m_new));
+                        const float x0 = fmaf(__uint_as_float(r[c][2 * i]), sc, -m_new);
+                        const float x1 = fmaf(__uint_as_float(r[c][2 * i + 1]), sc, -m_new);
+                        const float e0 = ex2(x0), e1 = ex2(x1);
                         ls0 += e0;
                         ls1 += e1;
                         const __half2 h2 = __floats2half2_rn(e0, e1);
