@@ -10,14 +10,18 @@ from .attention import sdpa, sdpa_, sdpaplan
 from .context import Ctx, DeviceArray, DeviceCaps, Workspace, caps
 from .conv import convolution_, convsize, onebyone
 from .elementwise import act_, add_, clamp_
+from .execute import Model, execute_, foldgelu, hoistpermutes
+from .graph import Buffer, Graph, Op, evalshape, loadgraph
 from .kernelplans import AttnScalarPlan, Decline, FlashTCPlan, MMScalarPlan, MMTilePlan
 from .layernorm import add_layernorm_, layernorm_, native_layer_norm
 from .matmul import batchedmatmul_, matmul_, mmplan
+from .plan import Slab, alignup, checkslab, lifetimes, place, planslab
 from .shard import gather_shards, shard_range, shard_range_py
 
 __all__ = [
     "B200Error", "SO_PATH", "lib", "sdpa", "sdpa_", "sdpaplan", "Ctx", "DeviceArray", "DeviceCaps", "Workspace",
     "caps", "convolution_", "convsize", "onebyone", "act_", "add_", "clamp_", "AttnScalarPlan", "Decline",
     "FlashTCPlan", "MMScalarPlan", "MMTilePlan", "layernorm_", "add_layernorm_", "native_layer_norm", "batchedmatmul_", "matmul_",
-    "mmplan", "shard_range", "shard_range_py", "gather_shards",
+    "mmplan", "Model", "execute_", "hoistpermutes", "foldgelu", "Buffer", "Graph", "Op", "evalshape", "loadgraph",
+    "Slab", "alignup", "checkslab", "lifetimes", "place", "planslab", "shard_range", "shard_range_py", "gather_shards",
 ]

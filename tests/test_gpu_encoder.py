@@ -81,3 +81,33 @@ def test_config3_shape_one_layer_vs_oracle(ctx):
     enc, w, got = _run(ctx, cfg, x)
     ref = oracle_forward(cfg, w, x)
     assert relerr(got, ref) < 1e-2, describe(got, ref, 1e-2)
+
+
+def test_exported_graph_through_execute_equals_direct_calls(ctx):
+    """The same encoder as an exported-graph JSON, run by Model/execute! with the static slab plan and
+    the load-time rewrites, must give the op-by-op pass bit for bit — planned, with no allocation
+    outside the plan except the transposed-weight staging it never needs after hoisting."""
+    import json
+
+    from juliavision_b200.encoder_graph import encoder_graph
+    from juliavision_b200.execute import Model
+    from juliavision_b200.graph import loadgraph
+    cfg = EncoderConfig(layers=2, d_model=256, heads=4, ffn=1024, tokens=300)
+    w = init_weights(cfg)
+    x = np.float16(np.random.default_rng(6).standard_normal((cfg.tokens, cfg.d_model)))
+    g, wts = encoder_graph(cfg, w)
+    graph = loadgraph(json.loads(json.dumps(g)))
+    model = Model(ctx, graph, wts)
+    assert model.rewrites == dict(hoistpermutes=6 * cfg.layers, foldgelu=cfg.layers)
+    (out,) = model(x.reshape(1, cfg.tokens, cfg.d_model))
+    ctx.synchronize()
+    got = out.to_host().reshape(cfg.tokens, cfg.d_model)
+    _, _, plain = _run(ctx, cfg, x, fused=False)
+    assert np.array_equal(got, plain)
+    from juliavision_b200.plan import escaping
+    esc = escaping(model.graph)
+    assert all(k.rsplit('.', 1)[0] in esc for k in model.planmisses), model.planmisses   # only the escaping output misses the slab
+    # and unrewritten (t(W) views materialised per call, gelu as its own op): same values
+    (out2,) = Model(ctx, graph, wts, rewrite=False)(x.reshape(1, cfg.tokens, cfg.d_model))
+    ctx.synchronize()
+    assert np.array_equal(out2.to_host().reshape(cfg.tokens, cfg.d_model), plain)
