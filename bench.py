@@ -57,7 +57,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -162,6 +162,33 @@ def kernel_figures(ctx, jv, pk, quick: bool):
                                                   frac_of_measured_peak=round(tf / pk["tflops"], 4),
                                                   frac_of_spec_2250=round(tf / 2250.0, 4))
 
+    # config-4 pieces (Hiera-B+-shaped 1024^2 image): the 7x7 stride-4 stem convolution lowered to the GEMM,
+    # and stage-1 windowed attention (8x8 windows = 64 tokens, 2 heads of 56, 1024 windows as the batch axis)
+    x = ctx.toback(np.float16(rng.random((1, 3, 1024, 1024), dtype=np.float32)))
+    w = ctx.toback(np.float16(rng.standard_normal((112, 3, 7, 7), dtype=np.float32) * 0.02))
+    cb = ctx.toback(np.float16(rng.standard_normal(112, dtype=np.float32) * 0.02))
+    co = ctx.allocate(np.float16, 256, 256, 112, 1)
+
+    def conv():
+        ctx.ws.reset()
+        jv.convolution_(ctx, co, x, w, cb, (4, 4), (3, 3), (1, 1), 1)
+
+    for _ in range(3):
+        conv()
+    ctx.synchronize()
+    ms = time_region(ctx, conv, 20)
+    out["conv_stem_1024x1024x3_7x7s4_to_112"] = dict(ms=round(ms, 5), tflops=round(2.0 * 65536 * 147 * 112 / ms / 1e9, 2),
+                                                     note="im2col (19 MB) + GEMM; HBM/latency-bound, not tensor-bound")
+    Bw, Hw, Lw, Ew = 1024, 2, 64, 56
+    q, k, v = (ctx.toback(np.float16(rng.standard_normal((Bw, Hw, Lw, Ew), dtype=np.float32))) for _ in range(3))
+    ow = ctx.allocate(np.float16, Ew, Lw, Hw, Bw)
+    watt = lambda: jv.sdpa(ctx, q, k, v, None, 1.0 / np.sqrt(Ew), out=ow)
+    for _ in range(3):
+        watt()
+    ctx.synchronize()
+    ms = time_region(ctx, watt, 20)
+    out["attention_windowed_B1024_H2_L64_E56"] = dict(ms=round(ms, 5), tflops=round(4.0 * Lw * Lw * Ew * Hw * Bw / ms / 1e9, 1))
+
     # layer norm: bandwidth on a tensor larger than L2 (65536 groups x 1280, fp16 in/out)
     groups, Cn = 65536, 1280
     a = ctx.toback(np.float16(rng.standard_normal((groups, Cn), dtype=np.float32)))
@@ -228,7 +255,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=32, help="encoder depth (32 = the named config)")

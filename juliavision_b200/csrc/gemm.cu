@@ -434,6 +434,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         for (int t = 0; t < 16; ++t) v[t] = __uint_as_float(r[t]) + rbias;
                     }
                 }
+                if (ew == 0 && lane == 0 && it == 0 && i == 0) GEMM_TRACE(20);   // first slab in registers
                 if (contributor) {
                     // Leave the raw fp32 accumulator slab for the finisher: [quarter q][lane] float4,
                     // so each store instruction of the warp writes 512 contiguous bytes.
@@ -513,6 +514,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                     }
                 }
                 __syncwarp();
+                if (ew == 0 && lane == 0 && it == 0 && i == 0) GEMM_TRACE(21);   // first slab converted and staged
                 // shared -> global, four lanes per row: lane l moves piece l%4 of rows l/4, l/4+8, ...
                 constexpr int EPP = 16 / (int)sizeof(OutT);  // elements per 16-byte piece
                 const int pj = lane & 3;
@@ -534,6 +536,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                     }
                 }
                 __syncwarp(); // the slab is free for the next round
+                if (ew == 0 && lane == 0 && it == 0 && i == 0) GEMM_TRACE(22);   // first slab stored
             }
             if (contributor) {
                 __threadfence();

@@ -134,3 +134,27 @@ def test_linearity_at_full_size(ctx):
     X1 = rng.integers(-2, 3, (tokens, K)).astype(np.float16)
     y1, y2, y12 = (linear_gpu(ctx, x, W2, out_dtype=np.float32) for x in (X1, X2, X1 + X2))
     assert np.array_equal(y1 + y2, y12)           # integer-valued: every partial sum is exact
+
+
+@pytest.mark.parametrize("tile", ["256x2", "128x2", "256x1", "128x1", "64x1", "256x2s", "128x2s", "256x1s", "64x1s"])
+def test_every_tile_shape_and_schedule(ctx, ora, tile, monkeypatch):
+    """The planner picks one (tile width, CTAs per tile, schedule) per call; the debugging override
+    forces each of them in turn — CTA pairs, single CTAs, whole-tile and stream-K schedules (a
+    trailing `s`) — on shapes with ragged tails, several tiles per worker and tiles cut across
+    workers.  All must agree with the oracle like the planner's own choice does."""
+    monkeypatch.setenv("B200_GEMM_TILE", tile)
+    rng = np.random.default_rng(hash(tile) % 1000)
+    for tokens, out, K in ((1500, 1280, 1280), (700, 5120, 640), (300, 1000, 4096), (4096, 3072, 768)):
+        X, Wt, b = _case(rng, tokens, out, K, scale=0.25)
+        got = linear_gpu(ctx, X, Wt, b, epi="gelu")
+        ref = ora.linear(X, Wt, b, epi="gelu")
+        assert relerr(got, ref) < TOL, (tile, tokens, out, K, describe(got, ref, TOL))
+
+
+def test_streamk_is_deterministic(ctx, monkeypatch):
+    monkeypatch.setenv("B200_GEMM_TILE", "256x2s")
+    rng = np.random.default_rng(77)
+    X, Wt, b = _case(rng, 1500, 1280, 5120, scale=0.25)
+    a1 = linear_gpu(ctx, X, Wt, b)
+    a2 = linear_gpu(ctx, X, Wt, b)
+    assert np.array_equal(a1, a2)
