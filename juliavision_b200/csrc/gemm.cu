@@ -28,7 +28,7 @@ namespace b200 {
 
 constexpr int GEMM_BM = 128; // tokens per CTA (TMEM lanes)
 constexpr int GEMM_BK = 64;  // one 128-byte swizzle row of fp16
-constexpr int EPI_WARPS = 8;
+constexpr int EPI_WARPS = 16;
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS; // producer warp, UMMA warp, epilogue warps
 constexpr int SMEM_LIMIT = 232448; // 227 KB
 
@@ -44,7 +44,7 @@ template <int BN, typename OutT, int NCTA> struct GemmCfg {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int OUT_COLS = 128 / (int)sizeof(OutT); // columns per 128-byte staging row
     static constexpr int SUB_COLS = 64 / (int)sizeof(OutT);   // epilogue slab: 64 bytes of output per row
-    static constexpr int TAIL_BYTES = EPI_WARPS * (BN * 2 + 2048) + 256; // per-warp fp16 bias and slab, barriers
+    static constexpr int TAIL_BYTES = EPI_WARPS * (BN / (EPI_WARPS / 4) * 4 + 32 * 16 * (int)sizeof(OutT)) + 256; // per-warp fp32 bias of its own columns and one staged chunk; barriers
     static constexpr int STAGES_RAW = (SMEM_LIMIT - TAIL_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TAIL_BYTES;
@@ -184,7 +184,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         return;
     }
     __half* sbias = reinterpret_cast<__half*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sbias) + EPI_WARPS * (BN * 2 + 2048));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sbias) + EPI_WARPS * (BN / (EPI_WARPS / 4) * 4 + 32 * 16 * (int)sizeof(OutT)));
     uint64_t* full = bars;                     // [STAGES]  (pair: only the leader's are used)
     uint64_t* empty = bars + Cfg::STAGES;      // [STAGES]
     uint64_t* tfull = bars + 2 * Cfg::STAGES;  // [2]
@@ -331,18 +331,24 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         }
     } else {
         // ---------------------------------------------------------------- epilogue
-        // Eight warps, two per TMEM lane quadrant; the two of a quadrant take alternate slabs of
-        // SUB columns.  Per slab: TMEM -> registers -> +bias, round, activation -> a warp-private
-        // swizzled shared slab (32 rows x 64 B) -> read back transposed so that four lanes cover 64
-        // contiguous bytes of one output row -> 16-byte global stores.  Warps never wait for one
-        // another and nothing is left in flight that a later step would have to wait for.
-        constexpr int SUB = Cfg::SUB_COLS;     // columns per slab: 64 bytes of output per row
-        const int ew = warp - 2;               // 0..7
+        // Sixteen warps, four per TMEM lane quadrant, each taking every fourth chunk of 16 columns.
+        // Per chunk: tcgen05.ld -> +bias, round, activation -> a warp-private swizzled shared slab
+        // (32 rows x 16 columns) -> read back transposed (several lanes per output row) -> 16-byte
+        // global stores.  Each step is a short dependent chain, so the throughput comes from the
+        // four warps per scheduler taking turns; warps never wait for one another.
+        constexpr int CH = 16;                 // columns per chunk (one tcgen05.ld.32x32b.x16)
+        constexpr int NPART = EPI_WARPS / 4;   // warps sharing a lane quadrant
+        constexpr int NCH = BN / NPART / CH;   // chunks one warp owns of a tile
+        constexpr int RB = CH * (int)sizeof(OutT);  // staged bytes per row and chunk
+        constexpr int PPR = RB / 16;           // 16-byte pieces per staged row
+        constexpr int EPP = 16 / (int)sizeof(OutT); // elements per piece
+        const int ew = warp - 2;               // 0..15
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
-        const int half = ew >> 2;              // which alternate slabs
+        const int part = ew >> 2;              // which chunks of the quadrant's rows
         const int row = quad * 32 + lane;      // token row inside this CTA's half of the tile
-        uint8_t* wstg = reinterpret_cast<uint8_t*>(sbias + EPI_WARPS * BN) + ew * 2048;
-        __half* wbias = sbias + ew * BN;
+        uint8_t* wstg = reinterpret_cast<uint8_t*>(sbias) + EPI_WARPS * (BN / NPART) * 4 + ew * (32 * RB);
+        float* wbias = reinterpret_cast<float*>(sbias) + ew * (BN / NPART);   // fp32 bias of this warp's own columns
+        auto chunk_col = [&](int c) { return (NPART * c + part) * CH; };
         int64_t it = 0;
         SegIter seg;
         for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); seg.valid(); seg.next(), ++it) {
@@ -364,7 +370,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                        SegIter::range_start(units, worker + 1 + ncontrib, nworkers) < tile_end)
                     ++ncontrib;
             }
-            constexpr int PART_PER_WARP = (BN / 2) * 32;                 // floats one epilogue warp owns of a tile
+            constexpr int PART_PER_WARP = (BN / NPART) * 32;             // floats one epilogue warp owns of a tile
             const int64_t my_slot = ((int64_t)worker * NCTA + rank) * EPI_WARPS + ew;
             bool sk_ok = true;
             if (ncontrib > 0) {
@@ -389,23 +395,15 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                 }
                 sk_ok = !__any_sync(0xffffffffu, !sk_ok);
             }
-
-            // The first contributor's slab is fetched one slab ahead of its use, so the L2 round trip
-            // runs under the previous slab's conversion and stores.
-            float4 pf[SUB / 4];
-            auto fetch_part = [&](int c, int i) {
-                const int64_t slot = ((int64_t)(worker + 1 + c) * NCTA + rank) * EPI_WARPS + ew;
-                const float4* src = reinterpret_cast<const float4*>(p.sk_part + slot * PART_PER_WARP + (size_t)i * (SUB * 32));
-#pragma unroll
-                for (int q = 0; q < SUB / 4; ++q) pf[q] = __ldcg(src + q * 32 + lane);
-            };
-            if (ncontrib > 0 && sk_ok) fetch_part(0, 0);
+            const bool collect = ncontrib > 0 && sk_ok;
 
             __syncwarp(); // the previous tile's readers of wbias are done
-            for (int j = lane; j < BN; j += 32)
-                wbias[j] = (p.bias != nullptr && !p.bias_per_n && m0 + j < p.M) ? p.bias[m0 + j] : __float2half(0.f);
-            const float rbias = (!contributor && p.bias != nullptr && p.bias_per_n && n0 + row < p.N)
-                                    ? __half2float(p.bias[n0 + row]) : 0.f;   // the finisher adds the bias
+            for (int j = lane; j < BN / NPART; j += 32) {   // wbias[c*CH + t] = bias of column chunk_col(c) + t
+                const int col = chunk_col(j / CH) + (j % CH);
+                wbias[j] = (p.bias != nullptr && !p.bias_per_n && m0 + col < p.M) ? __half2float(p.bias[m0 + col]) : 0.f;
+            }
+            const bool row_bias = !contributor && p.bias != nullptr && p.bias_per_n;   // the finisher adds the bias
+            const float rbias = (row_bias && n0 + row < p.N) ? __half2float(p.bias[n0 + row]) : 0.f;
             const bool got = mbar_wait(&tfull[acc], aph, p.d_status, KST_WAIT_TMEM_FULL, abort_flag);
             if (__any_sync(0xffffffffu, !got)) break; // one answer per warp
             tc_fence_after();
@@ -413,80 +411,79 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
 
             OutT* gtile = p.out + (size_t)batch * p.strideO + (size_t)(n0 + quad * 32) * p.ldo + m0;
             const int rows_valid = (int)(p.N - (n0 + quad * 32));   // rows of this warp's slab inside the output
-            constexpr int NSLAB = BN / SUB / 2;
+            const uint32_t tacc = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
+            const int act_kind = p.epilogue;
+            const int sw = (lane / (8 / PPR)) % PPR;   // piece j of staged row r sits at piece j ^ swizzle(r)
+            uint8_t* rowp = wstg + lane * RB;
+
 #pragma unroll 1
-            for (int i = 0; i < NSLAB; ++i) {
-                const int col0 = (2 * i + half) * SUB;
-                float v[SUB];
+            for (int c = 0; c < NCH; ++c) {
+                const int col0 = chunk_col(c);
+                float v[CH];
                 {
-                    const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN + col0;
-                    if constexpr (SUB == 32) {
-                        uint32_t r[32];
-                        tmem_ld32(taddr, r);
-                        tmem_wait_ld();
+                    uint32_t r[CH];
+                    tmem_ld16(tacc + col0, r);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int t = 0; t < 32; ++t) v[t] = __uint_as_float(r[t]) + rbias;
-                    } else {
-                        uint32_t r[16];
-                        tmem_ld16(taddr, r);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int t = 0; t < 16; ++t) v[t] = __uint_as_float(r[t]) + rbias;
-                    }
+                    for (int t = 0; t < CH; ++t) v[t] = __uint_as_float(r[t]);
                 }
-                if (ew == 0 && lane == 0 && it == 0 && i == 0) GEMM_TRACE(20);   // first slab in registers
-                if (contributor) {
-                    // Leave the raw fp32 accumulator slab for the finisher: [quarter q][lane] float4,
-                    // so each store instruction of the warp writes 512 contiguous bytes.
-                    float4* dst = reinterpret_cast<float4*>(p.sk_part + my_slot * PART_PER_WARP + (size_t)i * (SUB * 32));
-#pragma unroll
-                    for (int q = 0; q < SUB / 4; ++q)
-                        dst[q * 32 + lane] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                } else if (ncontrib > 0 && sk_ok) {
-                    for (int c = 0; c < ncontrib; ++c) {
-                        if (c > 0) fetch_part(c, i);
-#pragma unroll
-                        for (int q = 0; q < SUB / 4; ++q) {
-                            v[4 * q] += pf[q].x;
-                            v[4 * q + 1] += pf[q].y;
-                            v[4 * q + 2] += pf[q].z;
-                            v[4 * q + 3] += pf[q].w;
-                        }
-                    }
-                    if (i + 1 < NSLAB) fetch_part(0, i + 1);
-                }
-                if (i == NSLAB - 1) {
+                if (c == NCH - 1) {
                     // This warp has read all it needs of the accumulator: hand it back (leader CTA).
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {
-                        if constexpr (NCTA == 2) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
+                        if constexpr (NCTA == 2) mbar_arrive_cluster_cta_release(mapa_u32(smem_u32(&tempty[acc]), 0));
                         else mbar_arrive(&tempty[acc]);
                     }
                 }
-                if (contributor || m0 + col0 >= p.M || rows_valid <= 0) continue; // nothing to write to the output
+                if (row_bias) {
+#pragma unroll
+                    for (int t = 0; t < CH; ++t) v[t] += rbias;
+                }
+                if (contributor) {
+                    // Leave the raw fp32 accumulator chunk for the finisher: [quarter q][lane] float4,
+                    // so each store instruction of the warp writes 512 contiguous bytes.
+                    float4* dst = reinterpret_cast<float4*>(p.sk_part + my_slot * PART_PER_WARP + (size_t)c * (CH * 32));
+#pragma unroll
+                    for (int q = 0; q < CH / 4; ++q)
+                        dst[q * 32 + lane] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    continue;
+                }
+                if (collect) {
+                    for (int k = 0; k < ncontrib; ++k) {
+                        const int64_t slot = ((int64_t)(worker + 1 + k) * NCTA + rank) * EPI_WARPS + ew;
+                        const float4* src = reinterpret_cast<const float4*>(p.sk_part + slot * PART_PER_WARP + (size_t)c * (CH * 32));
+#pragma unroll
+                        for (int q = 0; q < CH / 4; ++q) {
+                            const float4 f = __ldcg(src + q * 32 + lane);
+                            v[4 * q] += f.x;
+                            v[4 * q + 1] += f.y;
+                            v[4 * q + 2] += f.z;
+                            v[4 * q + 3] += f.w;
+                        }
+                    }
+                }
+                if (m0 + col0 >= p.M || rows_valid <= 0) continue; // nothing to write to the output
 
-                // registers -> shared, lane = row; 16-byte piece j of row r sits at piece j ^ ((r>>1)&3)
-                uint8_t* rowp = wstg + lane * 64;
-                const int sw = (lane >> 1) & 3;
+                // registers -> shared, lane = row
+                const float* bc = wbias + c * CH;
                 if constexpr (sizeof(OutT) == 2) {
                     auto emit = [&](auto act) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
+                        for (int j = 0; j < 2; ++j) {
+                            const float4 b0 = *reinterpret_cast<const float4*>(bc + j * 8);
+                            const float4 b1 = *reinterpret_cast<const float4*>(bc + j * 8 + 4);
                             uint4 o;
                             __half2* h = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const int cidx = j * 8 + q * 2;
-                                const float2 bb = __half22float2(*reinterpret_cast<const __half2*>(&wbias[col0 + cidx]));
-                                // Round to fp16 first; the activation sees the rounded value.
-                                __half2 t = __floats2half2_rn(v[cidx] + bb.x, v[cidx + 1] + bb.y);
-                                h[q] = act(t);
-                            }
+                            // Round to fp16 first; the activation sees the rounded value.
+                            h[0] = act(__floats2half2_rn(v[j * 8 + 0] + b0.x, v[j * 8 + 1] + b0.y));
+                            h[1] = act(__floats2half2_rn(v[j * 8 + 2] + b0.z, v[j * 8 + 3] + b0.w));
+                            h[2] = act(__floats2half2_rn(v[j * 8 + 4] + b1.x, v[j * 8 + 5] + b1.y));
+                            h[3] = act(__floats2half2_rn(v[j * 8 + 6] + b1.z, v[j * 8 + 7] + b1.w));
                             *reinterpret_cast<uint4*>(rowp + ((j ^ sw) << 4)) = o;
                         }
                     };
-                    switch (p.epilogue) {
+                    switch (act_kind) {
                         case B200_EPI_RELU: emit([](__half2 t) { return __hmax2(t, __float2half2_rn(0.f)); }); break;
                         case B200_EPI_GELU:
                             emit([](__half2 t) {
@@ -505,25 +502,25 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                 } else {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
+                        const float4 b = *reinterpret_cast<const float4*>(bc + j * 4);
                         float4 o;
-                        o.x = apply_act(p.epilogue, v[j * 4 + 0] + __half2float(wbias[col0 + j * 4 + 0]));
-                        o.y = apply_act(p.epilogue, v[j * 4 + 1] + __half2float(wbias[col0 + j * 4 + 1]));
-                        o.z = apply_act(p.epilogue, v[j * 4 + 2] + __half2float(wbias[col0 + j * 4 + 2]));
-                        o.w = apply_act(p.epilogue, v[j * 4 + 3] + __half2float(wbias[col0 + j * 4 + 3]));
+                        o.x = apply_act(act_kind, v[j * 4 + 0] + b.x);
+                        o.y = apply_act(act_kind, v[j * 4 + 1] + b.y);
+                        o.z = apply_act(act_kind, v[j * 4 + 2] + b.z);
+                        o.w = apply_act(act_kind, v[j * 4 + 3] + b.w);
                         *reinterpret_cast<float4*>(rowp + ((j ^ sw) << 4)) = o;
                     }
                 }
-                __syncwarp();
-                if (ew == 0 && lane == 0 && it == 0 && i == 0) GEMM_TRACE(21);   // first slab converted and staged
-                // shared -> global, four lanes per row: lane l moves piece l%4 of rows l/4, l/4+8, ...
-                constexpr int EPP = 16 / (int)sizeof(OutT);  // elements per 16-byte piece
-                const int pj = lane & 3;
+                __syncwarp();   // the staged chunk is visible to the lanes that will store it
+
+                // shared -> global: PPR lanes per row, 32/PPR rows per instruction.
+                const int pj = lane % PPR;
                 const int colp = col0 + pj * EPP;             // first feature column of this lane's piece
                 const int cvalid = (int)(p.M - m0) - colp;    // columns of the piece inside the output
 #pragma unroll
-                for (int rr = 0; rr < 4; ++rr) {
-                    const int r = (lane >> 2) + 8 * rr;
-                    const uint4 piece = *reinterpret_cast<const uint4*>(wstg + r * 64 + ((pj ^ ((r >> 1) & 3)) << 4));
+                for (int rr = 0; rr < PPR; ++rr) {
+                    const int r = lane / PPR + (32 / PPR) * rr;
+                    const uint4 piece = *reinterpret_cast<const uint4*>(wstg + r * RB + ((pj ^ ((r / (8 / PPR)) % PPR)) << 4));
                     if (r < rows_valid && cvalid > 0) {
                         OutT* g = gtile + (size_t)r * p.ldo + colp;
                         if (cvalid >= EPP) {
@@ -535,8 +532,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         }
                     }
                 }
-                __syncwarp(); // the slab is free for the next round
-                if (ew == 0 && lane == 0 && it == 0 && i == 0) GEMM_TRACE(22);   // first slab stored
+                __syncwarp(); // the slab is free for the next chunk
             }
             if (contributor) {
                 __threadfence();

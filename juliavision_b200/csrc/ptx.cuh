@@ -351,6 +351,12 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t local_smem_addr, uint32_t 
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Same arrival with the default semantics (release at CTA scope): enough where the barrier only hands
+// tensor memory back (ordered by the tcgen05 fences), and it does not wait for the warp's earlier
+// global stores to become visible cluster-wide, which the cluster-scope release above does.
+__device__ __forceinline__ void mbar_arrive_cluster_cta_release(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
