@@ -165,7 +165,17 @@ int b200_attention_f16(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t
 int b200_attention_f16_strided(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
                                const b200_strided4* q, const b200_strided4* k, const b200_strided4* v,
                                const b200_strided4* out, int out_dtype, float scale);
-/* flashcm_plan (flash.jl:1322-1374): B200_OK or the Decline reason. */
+/* Same, with the additive mask of _scaled_dot_product_efficient_attention (ops.jl:1365-1375,
+ * attention.jl:55-59): bias is fp16 in the graph's own (Lk,Lq,H,B) order, stride[] = element strides
+ * along Lk, Lq, H, B with 0 on a broadcast (size-1) axis; bias == NULL or bias->ptr == NULL means no
+ * mask.  The mask is added to the scaled fp32 score; -inf entries block a key, and a row whose keys
+ * are all blocked comes out as zeros (attn_softmax, attention.jl:73-100).  The reference declines a
+ * bias on its fused path (flashcm_plan -> Decline(:bias)) and runs three passes; here it stays fused. */
+int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
+                            const b200_strided4* q, const b200_strided4* k, const b200_strided4* v,
+                            const b200_strided4* bias, const b200_strided4* out, int out_dtype, float scale);
+/* flashcm_plan (flash.jl:1322-1374): B200_OK or the Decline reason (has_bias is accepted and ignored:
+ * a mask does not decline here). */
 int b200_attention_f16_supported(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
                                  const int64_t* qstride, const int64_t* kstride,
                                  const int64_t* vstride, int has_bias);

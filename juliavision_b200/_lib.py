@@ -79,6 +79,8 @@ SIGNATURES = {
                                   C.POINTER(Strided4), _vp, _i32, _f32]),
     "b200_attention_f16_strided": (_i32, [_vp, _i64, _i64, _i64, _i64, _i64, C.POINTER(Strided4), C.POINTER(Strided4),
                                           C.POINTER(Strided4), C.POINTER(Strided4), _i32, _f32]),
+    "b200_attention_f16_bias": (_i32, [_vp, _i64, _i64, _i64, _i64, _i64, C.POINTER(Strided4), C.POINTER(Strided4),
+                                       C.POINTER(Strided4), C.POINTER(Strided4), C.POINTER(Strided4), _i32, _f32]),
     "b200_attention_f16_supported": (_i32, [_i64, _i64, _i64, _i64, _i64, C.POINTER(_i64), C.POINTER(_i64),
                                             C.POINTER(_i64), _i32]),
     "b200_layernorm": (_i32, [_vp, _i64, _i64, _vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _f32]),

@@ -2,7 +2,9 @@
 kernels/extern/flash.jl:1322-1484).
 
 q, k, v are (E, L, H, B) views with any strides along L, H, B (E contiguous); out is dense
-(E, Lq, H, B).  Non-causal; `bias` (an additive mask) is declined, as flashcm_plan does.
+(E, Lq, H, B).  Non-causal.  `bias` is the additive mask of the mem-efficient variant, fp16 in the
+graph's own (Lk, Lq, H, B) order with size-1 axes broadcasting (attention.jl:55-59); the reference
+declines it on its fused path and runs three passes, here it is added inside the fused kernel.
 """
 from __future__ import annotations
 
@@ -28,8 +30,6 @@ def _s4(a: DeviceArray) -> "_lib.Strided4":
 
 def sdpaplan(ctx: Ctx, q: DeviceArray, k: DeviceArray, v: DeviceArray, bias=None):
     """One decision before `out` exists: FlashTCPlan, AttnScalarPlan or Decline(reason)."""
-    if bias is not None:
-        return Decline("bias")
     if any(a.dtype != np.float16 for a in (q, k, v)):
         return Decline("eltype")
     if any(a.ndim != 4 for a in (q, k, v)):
@@ -38,6 +38,11 @@ def sdpaplan(ctx: Ctx, q: DeviceArray, k: DeviceArray, v: DeviceArray, bias=None
     Lk = k.shape[1]
     if k.shape != (E, Lk, H, B) or v.shape != (E, Lk, H, B):
         return Decline("extent")
+    if bias is not None:
+        if bias.dtype != np.float16:
+            return Decline("eltype")
+        if bias.ndim != 4 or any(have not in (1, want) for have, want in zip(bias.shape, (Lk, Lq, H, B))):
+            return Decline("bias")   # not broadcastable to (Lk, Lq, H, B)
     arr = lambda a: (C.c_int64 * 4)(*a.strides)
     rc = _lib.lib().b200_attention_f16_supported(E, Lq, Lk, H, B, arr(q), arr(k), arr(v), 0)
     if rc == _lib.OK and all(a.ptr % 16 == 0 for a in (q, k, v)):
@@ -63,8 +68,15 @@ def sdpa_(ctx: Ctx, plan, out: Optional[DeviceArray], q, k, v, bias, scale: floa
     # A dense out is the reference's contract; a strided view (e.g. token-major) folds the
     # permute copy that follows sdpa in the exported graphs into the store.
     qs, ks, vs, os_ = _s4(q), _s4(k), _s4(v), _s4(out)
-    check(_lib.lib().b200_attention_f16_strided(ctx.handle, E, Lq, Lk, H, B, C.byref(qs), C.byref(ks), C.byref(vs),
-                                                C.byref(os_), dtcode(out.dtype), float(scale)))
+    bs = None
+    if bias is not None:
+        bs = _s4(bias)
+        for i in range(4):
+            if bias.shape[i] == 1:
+                bs.stride[i] = 0       # bidx: a size-1 axis broadcasts
+    check(_lib.lib().b200_attention_f16_bias(ctx.handle, E, Lq, Lk, H, B, C.byref(qs), C.byref(ks), C.byref(vs),
+                                             C.byref(bs) if bs is not None else None, C.byref(os_),
+                                             dtcode(out.dtype), float(scale)))
     return out
 
 

@@ -54,6 +54,11 @@ struct AttnParams {
     int pair_ctas;      // CTAs [0, pair_ctas) own a whole pair; the rest own one tile of a pair each
     int* d_status;
     unsigned long long* trace;  // optional timeline of CTA (0,0,0) (globaltimer ns), null in normal use
+    // Additive mask of the mem-efficient variant (attention.jl:55-59), (Lk,Lq,H,B) fp16 with element
+    // strides (0 on a broadcast axis); null when absent.  bias_vec: rows can be read 8 keys at a time.
+    const __half* bias;
+    int64_t bsK, bsQ, bsH, bsB;
+    int bias_vec;
 };
 
 #define ATT_TRACE(slot)                                                                              \
@@ -85,6 +90,9 @@ __device__ __forceinline__ void tmem_st16_raw(uint32_t taddr, const uint32_t* r)
 //              other tile's softmax runs
 // P never touches shared memory: the softmax threads write it as packed fp16 into tensor memory and
 // the P V product takes its A operand from there, so the shared-memory port only feeds K and V.
+// BIAS: the scaled score gets an additive fp16 mask before the softmax; a row whose keys are all
+// blocked (-inf everywhere) comes out as zeros, as in attn_softmax (attention.jl:73-100).
+template <bool BIAS>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                         const __grid_constant__ CUtensorMap tmapK,
@@ -255,6 +263,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
             const uint32_t o_tmem = tmem_base + lane_base + ATT_O_COL + t * 64;
             const uint32_t p_tmem = tmem_base + lane_base + ATT_P_COL + t * 64;
             const float sc = p.scale_log2;
+            const float sce = BIAS ? 1.0f : sc;   // with a bias the scores are rescaled when it is added
             float m_run = -INFINITY, l_run = 0.f;
             bool ok = true;
             // Both tiles take the same time per block, and left alone they fall into step: both
@@ -282,6 +291,37 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 if (lane == 0) mbar_arrive(&s_empty[t]);
                 if (lane == 0 && quad == 0 && j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 3);  // S in registers
 
+                if constexpr (BIAS) {
+                    // r <- s * scale * log2(e) + bias * log2(e): from here on the scores are in the
+                    // exponent's own units and the scale below is one.
+                    const int lq = q0 + t * ATT_BR + row;
+                    const __half* brow = p.bias + (int64_t)(lq < p.Lq ? lq : 0) * p.bsQ + (int64_t)h * p.bsH +
+                                         (int64_t)b * p.bsB + (int64_t)j * ATT_BC * p.bsK;
+                    const float L2E = 1.4426950408889634f;
+                    if (p.bias_vec && nvalid >= ATT_BC) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                const uint4 w = __ldg(reinterpret_cast<const uint4*>(brow + c * 32 + g * 8));
+                                const __half2* hh = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    const float2 f = __half22float2(hh[u]);
+                                    r[c][g * 8 + 2 * u] = __float_as_uint(fmaf(__uint_as_float(r[c][g * 8 + 2 * u]), sc, f.x * L2E));
+                                    r[c][g * 8 + 2 * u + 1] = __float_as_uint(fmaf(__uint_as_float(r[c][g * 8 + 2 * u + 1]), sc, f.y * L2E));
+                                }
+                            }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const float bv = (c * 32 + i < nvalid) ? __half2float(brow[(int64_t)(c * 32 + i) * p.bsK]) : 0.f;
+                                r[c][i] = __float_as_uint(fmaf(__uint_as_float(r[c][i]), sc, bv * L2E));
+                            }
+                    }
+                }
                 // Row maximum of the raw scores (the scale is positive, so it commutes with max);
                 // eight independent chains instead of one 128-long dependent one.
                 if (nvalid < ATT_BC) {
@@ -307,9 +347,12 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 // it follows the true maximum lazily, moving (and rescaling O and the running sum)
                 // only when the maximum has grown by more than 2^8.  Any reference point gives the
                 // same quotient O / l; the lazy one makes rescales rare after the first blocks.
-                const float m_blk = mx * sc;
+                const float m_blk = mx * sce;
                 const float m_new = (m_blk > m_run + 8.0f) ? m_blk : m_run;
-                const float alpha = ex2(m_run - m_new); // 0 on the first block (m_run = -inf), else 1 or < 2^-8
+                // 0 on the first block (m_run = -inf), else 1 or < 2^-8.  With a mask a row may have seen
+                // nothing but -inf so far: then the reference point stays -inf and nothing is rescaled.
+                const float alpha = (BIAS && m_run == m_new) ? 1.0f : ex2(m_run - m_new);
+                const float m_sub = (BIAS && m_new == -INFINITY) ? 0.f : m_new;
 
                 // P's shared tile and O are both still in use by the previous block's P V.
                 if (j > 0 && !mbar_wait(&pv_done[t], (uint32_t)((j - 1) & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag)) {
@@ -347,8 +390,8 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float x0 = fmaf(__uint_as_float(r[c][2 * i]), sc, -m_new);
-                        const float x1 = fmaf(__uint_as_float(r[c][2 * i + 1]), sc, -m_new);
+                        const float x0 = fmaf(__uint_as_float(r[c][2 * i]), sce, -m_sub);
+                        const float x1 = fmaf(__uint_as_float(r[c][2 * i + 1]), sce, -m_sub);
                         const float e0 = ex2(x0), e1 = ex2(x1);
                         ls0 += e0;
                         ls1 += e1;
@@ -433,7 +476,8 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
 __global__ void attention_f16_scalar_kernel(int E, int Lq, int Lk, int H, int B, const __half* q, int64_t qsE, int64_t qsL, int64_t qsH, int64_t qsB,
                                             const __half* k, int64_t ksE, int64_t ksL, int64_t ksH, int64_t ksB,
                                             const __half* v, int64_t vsE, int64_t vsL, int64_t vsH, int64_t vsB,
-                                            void* out, int64_t osL, int64_t osH, int64_t osB, int out_f32, float scale) {
+                                            void* out, int64_t osL, int64_t osH, int64_t osB, int out_f32, float scale,
+                                            const __half* bias, int64_t bsK, int64_t bsQ, int64_t bsH, int64_t bsB) {
     const int lane = threadIdx.x & 31;
     const int64_t rowid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (rowid >= (int64_t)Lq * H * B) return;
@@ -443,13 +487,17 @@ __global__ void attention_f16_scalar_kernel(int E, int Lq, int Lk, int H, int B,
     const __half* qp = q + qsL * lq + qsH * h + qsB * b;
     const __half* kp = k + ksH * h + ksB * b;
     const __half* vp = v + vsH * h + vsB * b;
+    const __half* bp = bias ? bias + bsQ * lq + bsH * h + bsB * b : nullptr;
     float m = -INFINITY;
     for (int lk = lane; lk < Lk; lk += 32) {
         float a = 0.f;
         for (int e = 0; e < E; ++e) a = fmaf(__half2float(qp[qsE * e]), __half2float(kp[ksL * lk + ksE * e]), a);
-        m = fmaxf(m, a * scale);
+        a *= scale;
+        if (bp) a += __half2float(bp[bsK * lk]);
+        m = fmaxf(m, a);
     }
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (m == -INFINITY) m = 0.f;   // every key blocked: all exponentials are zero and the row divides by one
     // Each lane accumulates its own keys into E partial outputs held two per lane-pass.
     float l = 0.f;
     extern __shared__ float acc_sm[]; // [warps][E]
@@ -462,7 +510,9 @@ __global__ void attention_f16_scalar_kernel(int E, int Lq, int Lk, int H, int B,
         if (lk < Lk) {
             float a = 0.f;
             for (int e = 0; e < E; ++e) a = fmaf(__half2float(qp[qsE * e]), __half2float(kp[ksL * lk + ksE * e]), a);
-            pexp = __expf(a * scale - m);
+            a *= scale;
+            if (bp) a += __half2float(bp[bsK * lk]);
+            pexp = __expf(a - m);
             l += pexp;
             pexp = __half2float(__float2half_rn(pexp));
         }
@@ -523,7 +573,7 @@ extern "C" {
 int b200_attention_f16_supported(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
                                  const int64_t* qstride, const int64_t* kstride, const int64_t* vstride,
                                  int has_bias) {
-    if (has_bias) return B200_DECLINE_BIAS;
+    (void)has_bias;   // an additive mask no longer declines: b200_attention_f16_bias takes it
     if (!qstride || !kstride || !vstride) return B200_EINVAL;
     return tc_reason(E, Lq, Lk, H, B, qstride, kstride, vstride);
 }
@@ -543,7 +593,16 @@ int b200_attention_f16(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t
 int b200_attention_f16_strided(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
                                const b200_strided4* q, const b200_strided4* k, const b200_strided4* v,
                                const b200_strided4* o, int out_dtype, float scale) {
+    return b200_attention_f16_bias(ctx, E, Lq, Lk, H, B, q, k, v, nullptr, o, out_dtype, scale);
+}
+
+int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
+                            const b200_strided4* q, const b200_strided4* k, const b200_strided4* v,
+                            const b200_strided4* bias, const b200_strided4* o, int out_dtype, float scale) {
     B200_REQUIRE(ctx && q && k && v && o, B200_EINVAL, "attention: null argument");
+    const __half* bptr = (bias != nullptr) ? static_cast<const __half*>(bias->ptr) : nullptr;
+    const int64_t bs[4] = {bptr ? bias->stride[0] : 0, bptr ? bias->stride[1] : 0, bptr ? bias->stride[2] : 0,
+                           bptr ? bias->stride[3] : 0};
     void* out = const_cast<void*>(o->ptr);
     B200_REQUIRE(E >= 0 && Lq >= 0 && Lk >= 0 && H >= 0 && B >= 0, B200_EINVAL, "attention: negative extent");
     B200_REQUIRE(out_dtype == B200_F16 || out_dtype == B200_F32, B200_DECLINE_ELTYPE, "attention: out dtype %d",
@@ -575,14 +634,16 @@ int b200_attention_f16_strided(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk,
             (int)E, (int)Lq, (int)Lk, (int)H, (int)B, (const __half*)q->ptr, q->stride[0], q->stride[1],
             q->stride[2], q->stride[3], (const __half*)k->ptr, k->stride[0], k->stride[1], k->stride[2],
             k->stride[3], (const __half*)v->ptr, v->stride[0], v->stride[1], v->stride[2], v->stride[3], out,
-            o->stride[1], o->stride[2], o->stride[3], out_dtype == B200_F32, scale);
+            o->stride[1], o->stride[2], o->stride[3], out_dtype == B200_F32, scale, bptr, bs[0], bs[1], bs[2], bs[3]);
         ctx->launches++;
         B200_CUDA(cudaGetLastError());
         return B200_OK;
     }
     static bool attr_done[16] = {};
     if (!attr_done[ctx->device & 15]) {
-        B200_CUDA(cudaFuncSetAttribute(attention_f16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        B200_CUDA(cudaFuncSetAttribute(attention_f16_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       ATT_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(attention_f16_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        ATT_SMEM_BYTES));
         attr_done[ctx->device & 15] = true;
     }
@@ -599,6 +660,9 @@ int b200_attention_f16_strided(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk,
     p.out_f32 = out_dtype == B200_F32;
     p.d_status = ctx->d_status;
     p.trace = ctx->gemm_trace;
+    p.bias = bptr;
+    p.bsK = bs[0]; p.bsQ = bs[1]; p.bsH = bs[2]; p.bsB = bs[3];
+    p.bias_vec = bptr && bs[0] == 1 && al16(bptr) && bs[1] % 8 == 0 && bs[2] % 8 == 0 && bs[3] % 8 == 0;
     p.qpairs = (int)cdiv(Lq, 2 * ATT_BR);
     const int64_t pairs = (int64_t)p.qpairs * H * B;
     B200_REQUIRE(pairs < (1ll << 30), B200_DECLINE_EXTENT, "attention: too many query tiles");
@@ -609,8 +673,12 @@ int b200_attention_f16_strided(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk,
     int64_t nsplit = (pairs > sms && rem > 0 && 2 * rem <= sms && Lq % (2 * ATT_BR) == 0) ? rem : 0;
     p.pair_ctas = (int)(pairs - nsplit);
     dim3 grid((unsigned)(pairs + nsplit), 1, 1);
-    B200_CUDA(launch_dep(attention_f16_tc_kernel, grid, dim3(ATT_THREADS, 1, 1), ATT_SMEM_BYTES, ctx->stream, 1, tq, tk,
-                         tv, p));
+    if (bptr)
+        B200_CUDA(launch_dep(attention_f16_tc_kernel<true>, grid, dim3(ATT_THREADS, 1, 1), ATT_SMEM_BYTES, ctx->stream, 1,
+                             tq, tk, tv, p));
+    else
+        B200_CUDA(launch_dep(attention_f16_tc_kernel<false>, grid, dim3(ATT_THREADS, 1, 1), ATT_SMEM_BYTES, ctx->stream, 1,
+                             tq, tk, tv, p));
     ctx->launches++;
     return B200_OK;
 }

@@ -166,12 +166,14 @@ void ora_gemm_f64(int64_t M, int64_t N, int64_t K, const f16bits* A, int64_t lda
  * q,k,v are (E,L,H,B) with element strides s[0..3] (s[0] is the E stride);
  * scores are stored in the operands' dtype (fp16) between passes, the exponent is
  * stored as fp16 while the row sum adds the unrounded fp32 value, and the divide
- * happens in the apply pass.  out is dense (E,Lq,H,B).
+ * happens in the apply pass.  out is dense (E,Lq,H,B).  bias (may be NULL) is the additive
+ * mask of the mem-efficient variant, added to the scaled fp32 score before it is stored.
  */
 void ora_attention_threepass(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
                              const f16bits* q, const int64_t* qs, const f16bits* k,
                              const int64_t* ks, const f16bits* v, const int64_t* vs,
-                             void* out, int out_dtype, float scale) {
+                             void* out, int out_dtype, float scale, const f16bits* bias,
+                             const int64_t* bs) {
 #pragma omp parallel
     {
         f16bits* row = (f16bits*)malloc(sizeof(f16bits) * (size_t)Lk);
@@ -188,6 +190,9 @@ void ora_attention_threepass(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64
                         for (int64_t e = 0; e < E; ++e)
                             a = fmaf(h2f(qp[qs[0] * e]), h2f(kp[ks[0] * e]), a);
                         a *= scale;
+                        /* additive mask in the graph's own (Lk,Lq,H,B) order, size-1 axes
+                         * broadcast (stride 0): attention.jl:55-59 */
+                        if (bias) a += h2f(bias[bs[0] * lk + bs[1] * lq + bs[2] * h + bs[3] * b]);
                         row[lk] = f2h(a);
                         float r = h2f(row[lk]);
                         if (r > m) m = r;
@@ -229,7 +234,7 @@ void ora_attention_threepass(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64
 void ora_attention_ref(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
                        const f16bits* q, const int64_t* qs, const f16bits* k,
                        const int64_t* ks, const f16bits* v, const int64_t* vs, float* out,
-                       float scale) {
+                       float scale, const f16bits* bias, const int64_t* bs) {
 #pragma omp parallel
     {
         double* row = (double*)malloc(sizeof(double) * (size_t)Lk);
@@ -246,9 +251,14 @@ void ora_attention_ref(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
                         for (int64_t e = 0; e < E; ++e)
                             a += (double)h2f(qp[qs[0] * e]) * (double)h2f(kp[ks[0] * e]);
                         row[lk] = a * (double)scale;
+                        if (bias) row[lk] += (double)h2f(bias[bs[0] * lk + bs[1] * lq + bs[2] * h + bs[3] * b]);
                         if (row[lk] > m) m = row[lk];
                     }
                     double s = 0.0;
+                    if (!isfinite(m)) { /* every key blocked: zero row (attention.jl:73-100) */
+                        for (int64_t lk = 0; lk < Lk; ++lk) row[lk] = 0.0;
+                        s = 1.0;
+                    } else
                     for (int64_t lk = 0; lk < Lk; ++lk) {
                         row[lk] = exp(row[lk] - m);
                         s += row[lk];

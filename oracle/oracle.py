@@ -129,23 +129,37 @@ def _strides4(a: np.ndarray):
     return (C.c_int64 * 4)(s[3], s[2], s[1], s[0])
 
 
-def attention_threepass(q, k, v, scale, out_dtype=np.float32):
+def _bias_args(bias, B, H, Lq, Lk):
+    """bias: torch-order (B|1, H|1, Lq|1, Lk|1) fp16 additive mask or None -> (ptr, strides over Lk,Lq,H,B)."""
+    if bias is None:
+        return None, None
+    assert bias.dtype == np.float16 and bias.ndim == 4
+    for have, want in zip(bias.shape, (B, H, Lq, Lk)):
+        assert have in (1, want), f"bias shape {bias.shape} does not broadcast to {(B, H, Lq, Lk)}"
+    it = bias.itemsize
+    st = [0 if bias.shape[ax] == 1 else bias.strides[ax] // it for ax in (3, 2, 1, 0)]
+    return _p(bias), (C.c_int64 * 4)(*st)
+
+
+def attention_threepass(q, k, v, scale, out_dtype=np.float32, bias=None):
     """q,k,v: torch (B,H,L,E) fp16 arrays (any strides). Returns dense (B,H,Lq,E)."""
     B, H, Lq, E = q.shape
     Lk = k.shape[2]
     out = np.empty((B, H, Lq, E), dtype=out_dtype)
+    bp, bs = _bias_args(bias, B, H, Lq, Lk)
     lib().ora_attention_threepass(*_i64(E, Lq, Lk, H, B), _p(q), _strides4(q), _p(k), _strides4(k),
                                   _p(v), _strides4(v), _p(out), C.c_int(_dt(out_dtype)),
-                                  C.c_float(scale))
+                                  C.c_float(scale), bp, bs)
     return out
 
 
-def attention_ref(q, k, v, scale):
+def attention_ref(q, k, v, scale, bias=None):
     B, H, Lq, E = q.shape
     Lk = k.shape[2]
     out = np.empty((B, H, Lq, E), dtype=np.float32)
+    bp, bs = _bias_args(bias, B, H, Lq, Lk)
     lib().ora_attention_ref(*_i64(E, Lq, Lk, H, B), _p(q), _strides4(q), _p(k), _strides4(k),
-                            _p(v), _strides4(v), _p(out), C.c_float(scale))
+                            _p(v), _strides4(v), _p(out), C.c_float(scale), bp, bs)
     return out
 
 

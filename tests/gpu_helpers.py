@@ -50,13 +50,15 @@ def qkv_views(ctx, q, k, v):
     return outs
 
 
-def attention_gpu(ctx, q, k, v, scale, out_dtype=np.float16):
+def attention_gpu(ctx, q, k, v, scale, out_dtype=np.float16, bias=None):
+    """bias: torch-order (B|1, H|1, Lq|1, Lk|1) fp16 additive mask, uploaded as the (Lk,Lq,H,B) array."""
     dq, dk, dv = qkv_views(ctx, q, k, v)
     B, H, Lq, E = q.shape
     out = ctx.allocate(out_dtype, E, Lq, H, B)
     ctx.fill_bytes(out, 0xFF)
-    plan = jv.sdpaplan(ctx, dq, dk, dv, None)
-    jv.sdpa_(ctx, plan, out, dq, dk, dv, None, scale)
+    db = None if bias is None else ctx.toback(np.ascontiguousarray(bias))
+    plan = jv.sdpaplan(ctx, dq, dk, dv, db)
+    jv.sdpa_(ctx, plan, out, dq, dk, dv, db, scale)
     ctx.synchronize()
     return out.to_host(), plan
 

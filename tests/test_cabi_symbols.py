@@ -55,7 +55,7 @@ def test_supported_predicates_need_no_gpu():
     dense = lambda E, L_, H: i4(1, E, E * L_, E * L_ * H)
     assert L.b200_attention_f16_supported(64, 4096, 4096, 12, 1, dense(64, 4096, 12), dense(64, 4096, 12),
                                           dense(64, 4096, 12), 0) == 0
-    assert _lib.DECLINE[L.b200_attention_f16_supported(64, 8, 8, 1, 1, dense(64, 8, 1), dense(64, 8, 1),
-                                                       dense(64, 8, 1), 1)] == "bias"
+    # an additive mask does not decline: the fused kernel takes it (b200_attention_f16_bias)
+    assert L.b200_attention_f16_supported(64, 8, 8, 1, 1, dense(64, 8, 1), dense(64, 8, 1), dense(64, 8, 1), 1) == 0
     assert _lib.DECLINE[L.b200_attention_f16_supported(72, 8, 8, 1, 1, dense(72, 8, 1), dense(72, 8, 1),
                                                        dense(72, 8, 1), 0)] == "tiling"

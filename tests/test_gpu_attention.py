@@ -84,9 +84,52 @@ def test_head_dim_beyond_one_swizzle_row_takes_the_scalar_kernel(ctx, ora):
     assert relerr(got, ora.attention_ref(q, k, v, 1 / np.sqrt(72))) < TOL
 
 
+# torch (B,H,Lq,Lk,E) and the bias shape as torch (B|1, H|1, Lq|1, Lk|1)
+BIAS_CASES = [((2, 3, 256, 384, 64), (2, 3, 256, 384)),    # full mask, rows read 8 keys at a time
+              ((2, 3, 300, 200, 56), (2, 3, 300, 200)),    # ragged keys: the guarded scalar reads
+              ((2, 4, 256, 256, 64), (2, 1, 1, 256)),      # key-padding mask broadcast over heads and queries
+              ((1, 2, 130, 257, 32), (1, 1, 130, 257)),    # broadcast over heads, odd row stride
+              ((1, 2, 64, 64, 72), (1, 2, 64, 64))]        # head dim past one swizzle row: scalar kernel
+
+
+@pytest.mark.parametrize("shape,bshape", BIAS_CASES)
+def test_additive_bias_vs_oracle(ctx, ora, shape, bshape):
+    """The additive mask of the mem-efficient variant (attention.jl:55-59), which the reference runs
+    unfused: random finite values, -inf on a share of the keys, and some rows blocked entirely."""
+    B, H, Lq, Lk, E = shape
+    rng = np.random.default_rng(sum(shape) + sum(bshape))
+    q = np.float16(rng.standard_normal((B, H, Lq, E)))
+    k = np.float16(rng.standard_normal((B, H, Lk, E)))
+    v = np.float16(rng.standard_normal((B, H, Lk, E)))
+    bias = np.float16(rng.standard_normal(bshape))
+    bias[rng.random(bshape) < 0.3] = -np.inf
+    if bshape[2] > 1:
+        bias[:, :, 5, :] = -np.inf            # a query every key is hidden from
+        bias[:, :, bshape[2] - 1, : Lk // 2] = -np.inf
+    scale = 1 / np.sqrt(E)
+    for out_dtype in (np.float16, np.float32):
+        got, plan = attention_gpu(ctx, q, k, v, scale, out_dtype, bias=bias)
+        assert isinstance(plan, jv.FlashTCPlan if E <= 64 else jv.AttnScalarPlan), plan
+        assert np.all(np.isfinite(got))
+        ref = ora.attention_ref(q, k, v, scale, bias=bias)
+        assert relerr(got, ref) < TOL, describe(got, ref, TOL)
+        if bshape[2] > 1:
+            assert np.all(got[:, :, 5] == 0)   # all keys blocked: a zero row (attention.jl:73-100)
+        tp = ora.attention_threepass(q, k, v, scale, bias=bias)
+        assert relerr(got, tp) < 1e-2, describe(got, tp, 1e-2)
+
+
+def test_zero_bias_changes_nothing(ctx):
+    rng = np.random.default_rng(5)
+    q, k, v = (np.float16(rng.standard_normal((1, 2, 256, 64))) for _ in range(3))
+    plain, _ = attention_gpu(ctx, q, k, v, 0.125)
+    masked, _ = attention_gpu(ctx, q, k, v, 0.125, bias=np.zeros((1, 1, 256, 256), np.float16))
+    assert relerr(masked, plain) < 1e-3
+
+
 def test_declines(ctx):
     q = ctx.allocate(np.float16, 64, 128, 2, 1)
-    assert jv.sdpaplan(ctx, q, q, q, bias=q) == jv.Decline("bias")          # test_flash.jl:148-181
+    assert jv.sdpaplan(ctx, q, q, q, bias=q) == jv.Decline("bias")          # a mask that does not broadcast
     q32 = ctx.allocate(np.float32, 64, 128, 2, 1)
     assert jv.sdpaplan(ctx, q32, q32, q32) == jv.Decline("eltype")
     k = ctx.allocate(np.float16, 32, 128, 2, 1)

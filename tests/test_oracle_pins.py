@@ -194,3 +194,27 @@ def test_glue_ops(ora):
     b = np.float16([0.25, 2.0, 60000.0, -1.0])
     assert np.array_equal(ora.add(a, b), (a.astype(np.float32) + b.astype(np.float32)).astype(np.float16))
     assert np.array_equal(ora.clamp(a, -1.0, 2.0), np.float16([1.5, -1.0, 2.0, 2.0]))
+
+
+def test_attention_additive_bias_matches_a_float64_restatement(ora):
+    """attn_scores adds the mask to the scaled score (attention.jl:55-59); attn_softmax turns a row with
+    every key blocked into zeros (attention.jl:73-100).  Checked against plain numpy in float64."""
+    rng = np.random.default_rng(0)
+    B, H, Lq, Lk, E = 1, 2, 20, 30, 16
+    q = np.float16(rng.standard_normal((B, H, Lq, E)))
+    k = np.float16(rng.standard_normal((B, H, Lk, E)))
+    v = np.float16(rng.standard_normal((B, H, Lk, E)))
+    bias = np.float16(rng.standard_normal((1, 1, Lq, Lk)))
+    bias[rng.random(bias.shape) < 0.3] = -np.inf
+    bias[:, :, 5, :] = -np.inf
+    s = np.einsum("bhqe,bhke->bhqk", q.astype(np.float64), k.astype(np.float64)) * 0.25 + bias.astype(np.float64)
+    m = s.max(-1, keepdims=True)
+    m[~np.isfinite(m)] = 0
+    p = np.exp(s - m)
+    den = p.sum(-1, keepdims=True)
+    den[den == 0] = 1
+    want = np.einsum("bhqk,bhke->bhqe", p / den, v.astype(np.float64))
+    assert np.max(np.abs(ora.attention_ref(q, k, v, 0.25, bias=bias) - want)) < 1e-6
+    tp = ora.attention_threepass(q, k, v, 0.25, bias=bias)
+    assert np.max(np.abs(tp - want)) < 5e-3
+    assert np.all(tp[:, :, 5] == 0)
