@@ -250,6 +250,14 @@ int b200_conv2d_f16_noalloc(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, in
 int b200_add_f16(b200_ctx* ctx, const void* a, const void* b, void* out, int64_t n);
 int b200_clamp_f16(b200_ctx* ctx, const void* a, void* out, int64_t n, float lo, float hi);
 int b200_act_f16(b200_ctx* ctx, const void* a, void* out, int64_t n, int epilogue);
+/* max_pool2d_with_indices.default, values only (ops.jl:1329-1343, kernels/resample.jl:121-141):
+ * out[ox,oy,c,n] = max of x over the kx*ky window at (ox*sx-px, oy*sy-py), positions outside the
+ * image skipped.  x is (W,H,C,N) and out (OW,OH,C,N), OW = (W+2px-kx)/sx+1, each indexed through
+ * element strides {x, y, c, n}: {1,W,W*H,W*H*C} is the reference's planar layout, {C,C*W,1,C*W*H} a
+ * channels-last token array (eight channels per thread when that axis is contiguous in both). */
+int b200_maxpool2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t C, int64_t N, const void* x,
+                       const int64_t* xstride, void* out, const int64_t* ostride, int64_t kx, int64_t ky,
+                       int64_t sx, int64_t sy, int64_t px, int64_t py);
 /* permutedims!/contiguous of a 4-D array (execute.jl:257-277): out dense with shape
  * shape[0..3] (fastest first), element (i0,i1,i2,i3) read from
  * src[i0*s[0]+i1*s[1]+i2*s[2]+i3*s[3]]; elsize 2 or 4 bytes. */

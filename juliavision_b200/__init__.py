@@ -9,7 +9,7 @@ from ._lib import B200Error, SO_PATH, lib
 from .attention import sdpa, sdpa_, sdpaplan
 from .context import Ctx, DeviceArray, DeviceCaps, Workspace, caps
 from .conv import convolution_, convsize, onebyone
-from .elementwise import act_, add_, clamp_
+from .elementwise import act_, add_, clamp_, maxpool2d_
 from .execute import Model, execute_, foldgelu, hoistpermutes
 from .graph import Buffer, Graph, Op, evalshape, loadgraph
 from .kernelplans import AttnScalarPlan, Decline, FlashTCPlan, MMScalarPlan, MMTilePlan

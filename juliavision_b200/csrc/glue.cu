@@ -147,11 +147,109 @@ static int launch_permute(b200_ctx* ctx, const void* src, void* out, const int64
     return B200_OK;
 }
 
+// max_pool2d (reference kernels/resample.jl:121-141): out[ox,oy,c,n] = max over the window of
+// x[ix,iy,c,n], positions outside the image skipped, the running maximum starting at the type's
+// lowest value.  Both arrays are indexed (x, y, c, n) through element strides, so the planar layout
+// of the reference's call and a channels-last token array go through the same kernel; VEC = 8 takes
+// eight channels per thread when the channel axis is contiguous in both.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+maxpool2d_kernel(const __half* __restrict__ x, __half* __restrict__ out, int W, int H, int C, int OW, int OH, int64_t total,
+                 int64_t xs0, int64_t xs1, int64_t xs2, int64_t xs3, int64_t os0, int64_t os1, int64_t os2, int64_t os3,
+                 int kx, int ky, int sx, int sy, int px, int py, int c_fast) {
+    const int CV = C / VEC;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int ox, oy, c, n;
+        int64_t t = i;
+        if (c_fast) {   // channel fastest: neighbouring threads touch neighbouring channels
+            c = (int)(t % CV) * VEC; t /= CV;
+            ox = (int)(t % OW); t /= OW;
+            oy = (int)(t % OH); n = (int)(t / OH);
+        } else {
+            ox = (int)(t % OW); t /= OW;
+            oy = (int)(t % OH); t /= OH;
+            c = (int)(t % CV) * VEC; n = (int)(t / CV);
+        }
+        const int bx = ox * sx - px, by = oy * sy - py;
+        const __half* xp = x + (int64_t)c * xs2 + (int64_t)n * xs3;
+        if constexpr (VEC == 8) {
+            __half2 acc[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[u] = __half2half2(__ushort_as_half(0xFC00));   // -inf = typemin(Float16)
+            for (int dy = 0; dy < ky; ++dy) {
+                const int iy = by + dy;
+                if (iy < 0 || iy >= H) continue;
+                for (int dx = 0; dx < kx; ++dx) {
+                    const int ix = bx + dx;
+                    if (ix < 0 || ix >= W) continue;
+                    const uint4 w = *reinterpret_cast<const uint4*>(xp + (int64_t)ix * xs0 + (int64_t)iy * xs1);
+                    const __half2* hh = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) acc[u] = __hmax2_nan(acc[u], hh[u]);
+                }
+            }
+            *reinterpret_cast<uint4*>(out + (int64_t)ox * os0 + (int64_t)oy * os1 + (int64_t)c * os2 + (int64_t)n * os3) =
+                *reinterpret_cast<const uint4*>(acc);
+        } else {
+            __half acc = __ushort_as_half(0xFC00);
+            for (int dy = 0; dy < ky; ++dy) {
+                const int iy = by + dy;
+                if (iy < 0 || iy >= H) continue;
+                for (int dx = 0; dx < kx; ++dx) {
+                    const int ix = bx + dx;
+                    if (ix < 0 || ix >= W) continue;
+                    acc = __hmax_nan(acc, xp[(int64_t)ix * xs0 + (int64_t)iy * xs1]);
+                }
+            }
+            out[(int64_t)ox * os0 + (int64_t)oy * os1 + (int64_t)c * os2 + (int64_t)n * os3] = acc;
+        }
+    }
+}
+
 } // namespace b200
 
 using namespace b200;
 
 extern "C" {
+
+int b200_maxpool2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cn, int64_t N, const void* x, const int64_t* xstride,
+                       void* out, const int64_t* ostride, int64_t kx, int64_t ky, int64_t sx, int64_t sy, int64_t px,
+                       int64_t py) {
+    B200_REQUIRE(ctx && xstride && ostride, B200_EINVAL, "maxpool2d: null argument");
+    B200_REQUIRE(W >= 0 && H >= 0 && Cn >= 0 && N >= 0, B200_EINVAL, "maxpool2d: negative extent");
+    B200_REQUIRE(kx >= 1 && ky >= 1 && sx >= 1 && sy >= 1 && px >= 0 && py >= 0 && 2 * px <= kx && 2 * py <= ky,
+                 B200_EINVAL, "maxpool2d: window %lldx%lld stride %lldx%lld pad %lldx%lld", (long long)kx, (long long)ky,
+                 (long long)sx, (long long)sy, (long long)px, (long long)py);
+    B200_REQUIRE(W < (1ll << 30) && H < (1ll << 30) && Cn < (1ll << 30) && N < (1ll << 30), B200_DECLINE_EXTENT,
+                 "maxpool2d: extent");
+    if (W + 2 * px < kx || H + 2 * py < ky) return B200_OK;   // no output position
+    const int64_t OW = (W + 2 * px - kx) / sx + 1, OH = (H + 2 * py - ky) / sy + 1;
+    if (OW * OH * Cn * N == 0) return B200_OK;
+    B200_REQUIRE(x && out, B200_EINVAL, "maxpool2d: null array");
+    B200_CUDA(cudaSetDevice(ctx->device));
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    bool vec = xstride[2] == 1 && ostride[2] == 1 && Cn % 8 == 0 && al16(x) && al16(out);
+    for (int d = 0; d < 4; ++d)
+        if (d != 2) vec = vec && xstride[d] % 8 == 0 && ostride[d] % 8 == 0;
+    const int c_fast = ostride[2] == 1;
+    const int64_t total = OW * OH * (vec ? Cn / 8 : Cn) * N;
+    int64_t blocks = cdiv(total, 256);
+    const int64_t cap = (int64_t)ctx->prop.multiProcessorCount * 32;
+    if (blocks > cap) blocks = cap;
+    if (vec)
+        maxpool2d_kernel<8><<<(unsigned)blocks, 256, 0, ctx->stream>>>(
+            (const __half*)x, (__half*)out, (int)W, (int)H, (int)Cn, (int)OW, (int)OH, total, xstride[0], xstride[1],
+            xstride[2], xstride[3], ostride[0], ostride[1], ostride[2], ostride[3], (int)kx, (int)ky, (int)sx, (int)sy,
+            (int)px, (int)py, c_fast);
+    else
+        maxpool2d_kernel<1><<<(unsigned)blocks, 256, 0, ctx->stream>>>(
+            (const __half*)x, (__half*)out, (int)W, (int)H, (int)Cn, (int)OW, (int)OH, total, xstride[0], xstride[1],
+            xstride[2], xstride[3], ostride[0], ostride[1], ostride[2], ostride[3], (int)kx, (int)ky, (int)sx, (int)sy,
+            (int)px, (int)py, c_fast);
+    ctx->launches++;
+    B200_CUDA(cudaGetLastError());
+    return B200_OK;
+}
 
 int b200_add_f16(b200_ctx* ctx, const void* a, const void* b, void* out, int64_t n) {
     B200_REQUIRE(ctx && n >= 0 && (n == 0 || (a && b && out)), B200_EINVAL, "add: bad argument");

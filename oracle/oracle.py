@@ -231,3 +231,17 @@ def clamp(a, lo, hi):
     y = np.empty_like(a)
     lib().ora_clamp_f16(_p(a), _p(y), C.c_int64(a.size), C.c_float(lo), C.c_float(hi))
     return y
+
+
+def maxpool2d(x: np.ndarray, k, s, p=(0, 0)) -> np.ndarray:
+    """kernels/resample.jl:121-141 (maxpool): x torch (N,C,H,W); k, s, p = (x, y) pairs; positions
+    outside the image are skipped and the maximum starts from the lowest value of the type."""
+    N, Cn, H, W = x.shape
+    OW, OH = (W + 2 * p[0] - k[0]) // s[0] + 1, (H + 2 * p[1] - k[1]) // s[1] + 1
+    pad = np.full((N, Cn, H + 2 * p[1], W + 2 * p[0]), -np.inf, dtype=x.dtype)
+    pad[:, :, p[1]:p[1] + H, p[0]:p[0] + W] = x
+    out = np.full((N, Cn, OH, OW), -np.inf, dtype=x.dtype)
+    for dy in range(k[1]):
+        for dx in range(k[0]):
+            out = np.maximum(out, pad[:, :, dy:dy + (OH - 1) * s[1] + 1:s[1], dx:dx + (OW - 1) * s[0] + 1:s[0]])
+    return out

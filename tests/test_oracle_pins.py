@@ -218,3 +218,35 @@ def test_attention_additive_bias_matches_a_float64_restatement(ora):
     tp = ora.attention_threepass(q, k, v, 0.25, bias=bias)
     assert np.max(np.abs(tp - want)) < 5e-3
     assert np.all(tp[:, :, 5] == 0)
+
+
+def test_maxpool_oracle_matches_the_reference_loop(ora):
+    """resample.jl:121-141 restated as explicit loops on a small case (padding, stride != window)."""
+    rng = np.random.default_rng(1)
+    x = np.float16(rng.standard_normal((2, 3, 7, 9)))
+    k, s, p = (3, 2), (2, 1), (1, 0)
+    got = ora.maxpool2d(x, k, s, p)
+    N, Cn, H, W = x.shape
+    OW, OH = (W + 2 * p[0] - k[0]) // s[0] + 1, (H + 2 * p[1] - k[1]) // s[1] + 1
+    want = np.empty((N, Cn, OH, OW), np.float16)
+    for n in range(N):
+        for c in range(Cn):
+            for oy in range(OH):
+                for ox in range(OW):
+                    acc = -np.inf
+                    for ky in range(k[1]):
+                        for kx in range(k[0]):
+                            iy, ix = oy * s[1] - p[1] + ky, ox * s[0] - p[0] + kx
+                            if 0 <= iy < H and 0 <= ix < W:
+                                acc = max(acc, float(x[n, c, iy, ix]))
+                    want[n, c, oy, ox] = acc
+    assert np.array_equal(got, want)
+
+
+def test_hiera_reference_window_round_trip():
+    from oracle.hiera_ref import _partition, _unpartition
+    x = np.arange(2 * 8 * 8 * 3, dtype=np.float32).reshape(2, 8, 8, 3)
+    xw = _partition(x, 4)
+    assert xw.shape == (8, 16, 3)
+    assert np.array_equal(xw[1, 0], x[0, 0, 4])          # second window of the first row starts at column 4
+    assert np.array_equal(_unpartition(xw, 4, 2, 8), x)
