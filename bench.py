@@ -209,6 +209,23 @@ def kernel_figures(ctx, jv, pk, quick: bool):
     out["layernorm_65536x1280"] = dict(ms=round(ms, 5), gbs=round(byts / ms / 1e6, 1),
                                        frac_of_measured_hbm=round(byts / ms / 1e6 / pk["hbm_gbs"], 4),
                                        frac_of_spec_8000=round(byts / ms / 1e6 / 8000.0, 4))
+
+    # the whole Hiera-B+-shaped image encoder (1024x1024x3 in, 24 blocks, 32x32x896 out), one image and
+    # eight per pass, each pass replayed as a CUDA graph
+    from juliavision_b200.hiera import Hiera, HieraConfig
+    hcfg = HieraConfig()
+    for hb in (1, 8):
+        hm = Hiera(ctx, hcfg, batch=hb)
+        ctx.upload(hm.image, np.float16(rng.random((hb, hcfg.in_ch, hcfg.image, hcfg.image), dtype=np.float32)))
+        per_pass = hm.launches_per_pass()
+        hg = hm.capture()
+        for _ in range(2):
+            hg.replay()
+        ctx.synchronize()
+        ms = time_region(ctx, hg.replay, 3 if quick else 10)
+        out[f"hiera_bplus_1024_batch{hb}"] = dict(ms_per_img=round(ms / hb, 4), tflops=round(hcfg.flops(hb) / ms / 1e9, 1),
+                                                  launches_per_pass=per_pass)
+        del hm, hg
     return out
 
 
