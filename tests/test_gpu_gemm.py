@@ -158,3 +158,27 @@ def test_streamk_is_deterministic(ctx, monkeypatch):
     a1 = linear_gpu(ctx, X, Wt, b)
     a2 = linear_gpu(ctx, X, Wt, b)
     assert np.array_equal(a1, a2)
+
+
+@pytest.mark.parametrize("K", [768, 1280])
+@pytest.mark.parametrize("out", [1000, 3072, 5120])
+@pytest.mark.parametrize("tokens", [256, 4096, 65536])
+def test_sweep_rows_sampled_and_row_shards(ctx, ora, tokens, out, K):
+    """The scaling sweep's GEMM shapes (tokens 256..65536, out 1000/3072/5120 with 1000 ragged, K 768/1280).
+    A sample of rows against the oracle, and the row split the sharding layer makes: each shard computed on
+    its own equals the same rows of the whole product."""
+    rng = np.random.default_rng(tokens + out + K)
+    X = np.float16(rng.standard_normal((tokens, K), dtype=np.float32) * 0.05)
+    Wt = np.float16(rng.standard_normal((K, out), dtype=np.float32) * 0.05)
+    b = np.float16(rng.standard_normal(out, dtype=np.float32) * 0.05)
+    got = linear_gpu(ctx, X, Wt, b)
+    rows = np.sort(rng.choice(tokens, 48, replace=False))
+    ref = ora.linear(np.ascontiguousarray(X[rows]), Wt, b)
+    assert relerr(got[rows], ref) < TOL, describe(got[rows], ref, TOL)
+    world = 8
+    for rank in (0, 3, world - 1):
+        r0, r1 = jv.shard_range(tokens, world, rank, align=256)
+        if r1 > r0:
+            part = linear_gpu(ctx, np.ascontiguousarray(X[r0:r1]), Wt, b)
+            assert relerr(part, got[r0:r1]) < 1e-3
+            assert np.mean(part != got[r0:r1]) < 1e-3      # summation order may differ where a tile was split along K
