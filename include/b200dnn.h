@@ -250,6 +250,9 @@ int b200_conv2d_f16_noalloc(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, in
 int b200_add_f16(b200_ctx* ctx, const void* a, const void* b, void* out, int64_t n);
 int b200_clamp_f16(b200_ctx* ctx, const void* a, void* out, int64_t n, float lo, float hi);
 int b200_act_f16(b200_ctx* ctx, const void* a, void* out, int64_t n, int epilogue);
+/* _to_copy.default between fp16 and fp32 on dense arrays (ops.jl:342-358); round to nearest even
+ * on the way down, exact on the way up; equal dtypes are a device copy. */
+int b200_cast(b200_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n);
 /* max_pool2d_with_indices.default, values only (ops.jl:1329-1343, kernels/resample.jl:121-141):
  * out[ox,oy,c,n] = max of x over the kx*ky window at (ox*sx-px, oy*sy-py), positions outside the
  * image skipped.  x is (W,H,C,N) and out (OW,OH,C,N), OW = (W+2px-kx)/sx+1, each indexed through

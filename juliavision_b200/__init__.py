@@ -9,12 +9,13 @@ from ._lib import B200Error, SO_PATH, lib
 from .attention import sdpa, sdpa_, sdpaplan
 from .context import Ctx, DeviceArray, DeviceCaps, Workspace, caps
 from .conv import convolution_, convsize, onebyone
-from .elementwise import act_, add_, clamp_, maxpool2d_
-from .execute import Model, execute_, foldgelu, hoistpermutes
+from .elementwise import act_, add_, clamp_, maxpool2d_, to_copy_
+from .execute import Model, execute_, foldgelu, foldoutcasts, hoistpermutes
 from .graph import Buffer, Graph, Op, evalshape, loadgraph
 from .kernelplans import AttnScalarPlan, Decline, FlashTCPlan, MMScalarPlan, MMTilePlan
 from .layernorm import add_layernorm_, layernorm_, native_layer_norm
 from .matmul import batchedmatmul_, matmul_, mmplan
+from .safetensors import readsafetensors, safetensorsnames
 from .plan import Slab, alignup, checkslab, lifetimes, place, planslab
 from .shard import gather_shards, shard_range, shard_range_py
 
@@ -24,4 +25,5 @@ __all__ = [
     "FlashTCPlan", "MMScalarPlan", "MMTilePlan", "layernorm_", "add_layernorm_", "native_layer_norm", "batchedmatmul_", "matmul_",
     "mmplan", "Model", "execute_", "hoistpermutes", "foldgelu", "Buffer", "Graph", "Op", "evalshape", "loadgraph",
     "Slab", "alignup", "checkslab", "lifetimes", "place", "planslab", "shard_range", "shard_range_py", "gather_shards",
+    "maxpool2d_", "to_copy_", "foldoutcasts", "readsafetensors", "safetensorsnames",
 ]

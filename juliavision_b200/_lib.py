@@ -91,6 +91,7 @@ SIGNATURES = {
     "b200_add_f16": (_i32, [_vp, _vp, _vp, _vp, _i64]),
     "b200_clamp_f16": (_i32, [_vp, _vp, _vp, _i64, _f32, _f32]),
     "b200_act_f16": (_i32, [_vp, _vp, _vp, _i64, _i32]),
+    "b200_cast": (_i32, [_vp, _vp, _i32, _vp, _i32, _i64]),
     "b200_maxpool2d_f16": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64)] + [_i64] * 6),
     "b200_permute4": (_i32, [_vp, _vp, _vp, C.POINTER(_i64), C.POINTER(_i64), _i32]),
     "b200_shard_range": (_i32, [_i64, _i32, _i32, _i64, C.POINTER(_i64), C.POINTER(_i64)]),

@@ -87,6 +87,60 @@ static int launch_ew(b200_ctx* ctx, const void* a, const void* b, void* out, int
     return B200_OK;
 }
 
+// _to_copy between fp16 and fp32 (ops.jl:342-358): eight elements per thread when both ends are
+// 16-byte aligned, a scalar loop for the tail.
+template <typename SrcT, typename DstT>
+__global__ void __launch_bounds__(256)
+cast_kernel(const SrcT* __restrict__ src, DstT* __restrict__ dst, int64_t n, int vec) {
+    const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+    auto tof = [](SrcT v) -> float {
+        if constexpr (sizeof(SrcT) == 2) return __half2float(v);
+        else return v;
+    };
+    auto fromf = [](float v) -> DstT {
+        if constexpr (sizeof(DstT) == 2) return __float2half_rn(v);
+        else return v;
+    };
+    int64_t done = 0;
+    if (vec) {
+        const int64_t nv = n / 8;
+        for (int64_t i = tid; i < nv; i += nthreads) {
+            SrcT in[8];
+            DstT o[8];
+            if constexpr (sizeof(SrcT) == 2) {
+                *reinterpret_cast<uint4*>(in) = __ldg(reinterpret_cast<const uint4*>(src) + i);
+            } else {
+                *reinterpret_cast<uint4*>(in) = __ldg(reinterpret_cast<const uint4*>(src) + 2 * i);
+                *reinterpret_cast<uint4*>(in + 4) = __ldg(reinterpret_cast<const uint4*>(src) + 2 * i + 1);
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) o[q] = fromf(tof(in[q]));
+            if constexpr (sizeof(DstT) == 2) {
+                reinterpret_cast<uint4*>(dst)[i] = *reinterpret_cast<const uint4*>(o);
+            } else {
+                reinterpret_cast<uint4*>(dst)[2 * i] = *reinterpret_cast<const uint4*>(o);
+                reinterpret_cast<uint4*>(dst)[2 * i + 1] = *reinterpret_cast<const uint4*>(o + 4);
+            }
+        }
+        done = nv * 8;
+    }
+    for (int64_t i = done + tid; i < n; i += nthreads) dst[i] = fromf(tof(src[i]));
+}
+
+template <typename SrcT, typename DstT>
+static int launch_cast(b200_ctx* ctx, const void* src, void* dst, int64_t n) {
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const int vec = al(src) && al(dst);
+    int64_t blocks = cdiv(vec ? cdiv(n, 8) : n, 256);
+    const int64_t cap = (int64_t)ctx->prop.multiProcessorCount * 16;
+    if (blocks > cap) blocks = cap;
+    cast_kernel<SrcT, DstT><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const SrcT*)src, (DstT*)dst, n, vec);
+    ctx->launches++;
+    B200_CUDA(cudaGetLastError());
+    return B200_OK;
+}
+
 // Strided gather into a dense array: one thread per output element, output-coalesced.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -267,6 +321,18 @@ int b200_act_f16(b200_ctx* ctx, const void* a, void* out, int64_t n, int epilogu
                  epilogue);
     B200_CUDA(cudaSetDevice(ctx->device));
     return launch_ew<OP_ACT>(ctx, a, nullptr, out, n, 0.f, 0.f, epilogue);
+}
+int b200_cast(b200_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n) {
+    B200_REQUIRE(ctx && n >= 0 && (n == 0 || (src && dst)), B200_EINVAL, "cast: bad argument");
+    B200_REQUIRE((src_dtype == B200_F16 || src_dtype == B200_F32) && (dst_dtype == B200_F16 || dst_dtype == B200_F32),
+                 B200_DECLINE_ELTYPE, "cast: dtypes %d -> %d", src_dtype, dst_dtype);
+    if (n == 0) return B200_OK;
+    B200_CUDA(cudaSetDevice(ctx->device));
+    if (src_dtype == dst_dtype) {
+        B200_CUDA(cudaMemcpyAsync(dst, src, (size_t)n * (src_dtype == B200_F16 ? 2 : 4), cudaMemcpyDeviceToDevice, ctx->stream));
+        return B200_OK;
+    }
+    return src_dtype == B200_F16 ? launch_cast<__half, float>(ctx, src, dst, n) : launch_cast<float, __half>(ctx, src, dst, n);
 }
 int b200_permute4(b200_ctx* ctx, const void* src, void* out, const int64_t* shape, const int64_t* stride,
                   int elsize) {

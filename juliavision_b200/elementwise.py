@@ -30,6 +30,15 @@ def act_(ctx: Ctx, out: DeviceArray, a: DeviceArray, name: str) -> DeviceArray:
     return out
 
 
+def to_copy_(ctx: Ctx, out: DeviceArray, a: DeviceArray) -> DeviceArray:
+    """_to_copy.default: out = convert(eltype(out), a) for dense fp16/fp32 arrays (ops.jl:342-358)."""
+    from .context import dtcode
+    if not (a.isdense() and out.isdense() and a.size == out.size):
+        raise B200Error(16, "_to_copy: dense arrays of one length")
+    check(_lib.lib().b200_cast(ctx.handle, a.ptr, dtcode(a.dtype), out.ptr, dtcode(out.dtype), a.size))
+    return out
+
+
 def maxpool2d_(ctx: Ctx, out: DeviceArray, x: DeviceArray, k, s, p=(0, 0)) -> DeviceArray:
     """maxpool2d!(ctx, out, x, k, s, p) (kernels/resample.jl:141): x is indexed (x, y, c, n) and out
     (ox, oy, c, n), each through its own strides, so a planar array and a permuted view of a

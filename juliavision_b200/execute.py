@@ -5,7 +5,9 @@ Mirrors the reference's `Model` / `call` / `execute!` / `runop!` / `makeview` / 
 (DNNKernels/src/driver.jl:128-223, execute.jl:43-158,257-539, ops.jl:575-647,1114-1399) and two of
 its rewrite passes: `hoistpermutes` (hoistcasts.jl:62-112 — a `t`/`permute` view of a weight becomes a
 dense weight, which is what puts `addmm` on the tensor-core path) and the gelu half of `foldrelu`
-(foldrelu.jl:81-124 — `gelu(addmm(...))` becomes `addmm` with `attrs["act"] = "gelu"`).
+(foldrelu.jl:81-124 — `gelu(addmm(...))` becomes `addmm` with `attrs["act"] = "gelu"`), and
+`foldoutcasts` (foldoutcasts.jl:82-155 — a narrowing cast folded into the declared dtype of the layer
+norm or clone that feeds it).
 An op outside this set raises, as `runop!`'s fallback does (execute.jl:541-542).
 """
 from __future__ import annotations
@@ -20,7 +22,7 @@ from ._lib import B200Error
 from .attention import sdpa
 from .context import Ctx, DeviceArray
 from .conv import convolution_, convsize
-from .elementwise import act_, add_, clamp_
+from .elementwise import act_, add_, clamp_, maxpool2d_, to_copy_
 from .graph import Buffer, Graph, Op, evalshape
 from .layernorm import layernorm_
 from .matmul import _colmajor_2d, batchedmatmul_, matmul_
@@ -81,6 +83,70 @@ def foldgelu(graph: Graph) -> int:
     return n
 
 
+OUTCAST_PRODUCERS = ("native_layer_norm.default", "clone.default")
+
+
+def _viewchain(graph: Graph, id: str) -> List[str]:
+    """Buffer ids from `id` down to the first non-view buffer, `id` included (foldoutcasts.jl:54-62)."""
+    ids = [id]
+    for _ in range(16):
+        b = graph.buffers.get(ids[-1])
+        if b is None or b.kind != "view" or not b.of:
+            break
+        ids.append(b.of)
+    return ids
+
+
+def foldoutcasts(graph: Graph) -> int:
+    """A narrowing `_to_copy` whose input is produced by a layer norm or a clone and read by nothing
+    else: declare the producer's result in the narrow dtype and turn the cast's result into an alias
+    (foldoutcasts.jl:82-155).  The producer computes in fp32 either way and rounds once at its store,
+    so the values are the ones the cast produced.  Readers are counted through views."""
+    producer = {o.out: o for o in graph.ops}
+    reads: Dict[str, int] = {}
+    for o in graph.ops:
+        for i in o.ins:
+            r = _viewchain(graph, i)[-1]
+            reads[r] = reads.get(r, 0) + 1
+    for o in graph.outputs:
+        r = _viewchain(graph, o)[-1]
+        reads[r] = reads.get(r, 0) + 1
+    drop, n = set(), 0
+    for cast in graph.ops:
+        if cast.aten != "_to_copy.default" or len(cast.ins) != 1:
+            continue
+        chain = _viewchain(graph, cast.ins[0])
+        src = chain[-1]
+        p = producer.get(src)
+        ob, ib = graph.buffers.get(cast.out), graph.buffers.get(cast.ins[0])
+        if (p is None or p.aten not in OUTCAST_PRODUCERS or reads.get(src, 0) != 1 or ob is None or ib is None
+                or ob.kind != "transient" or list(ob.shape) != list(ib.shape)
+                or np.dtype(ob.dtype).itemsize >= np.dtype(ib.dtype).itemsize):
+            continue
+        ok = True
+        for id in chain:
+            b = graph.buffers[id]
+            if id == src and "dtypes" in b.attrs:
+                sel = graph.buffers[chain[max(0, len(chain) - 2)]]
+                ti = sel.attrs.get("arg1") if sel.kind == "view" and "getitem" in sel.viewop else None
+                if not isinstance(ti, int) or ti >= len(b.attrs["dtypes"]):
+                    ok = False
+                    break
+                b.attrs["dtypes"] = list(b.attrs["dtypes"])
+                b.attrs["dtypes"][ti] = ob.dtype
+            else:
+                b.dtype = ob.dtype
+        if not ok:
+            continue
+        graph.buffers[cast.out] = Buffer(cast.out, "view", list(ob.shape), ob.dtype, of=cast.ins[0], viewop="alias.default",
+                                         attrs=dict(ob.attrs))
+        drop.add(cast.id)
+        n += 1
+    if n:
+        graph.ops[:] = [o for o in graph.ops if o.id not in drop]
+    return n
+
+
 # ------------------------------------------------------------------------------ model
 class Model:
     """Model(graph, weights): rewrite, upload, plan (driver.jl:128-182). `weights` maps safetensors
@@ -91,10 +157,11 @@ class Model:
         self.ctx, self.dims = ctx, dims or {}
         self.graph = copy.deepcopy(graph)
         weights = dict(weights)
-        self.rewrites = dict(hoistpermutes=0, foldgelu=0)
+        self.rewrites = dict(hoistpermutes=0, foldgelu=0, foldoutcasts=0)
         if rewrite:
             self.rewrites["hoistpermutes"] = hoistpermutes(self.graph, weights)
             self.rewrites["foldgelu"] = foldgelu(self.graph)
+            self.rewrites["foldoutcasts"] = foldoutcasts(self.graph)
         self.weights: Dict[str, DeviceArray] = {}
         for b in self.graph.buffers.values():
             if b.kind == "weight":
@@ -222,13 +289,15 @@ def _op_bmm(run: _Run, op: Op):
 
 
 def _op_sdpa(run: _Run, op: Op):
-    q, k, v = (run.value(i) for i in op.ins[:3])           # ops.jl:1380-1391
-    if len(op.ins) > 3:
-        raise B200Error(19, "sdpa: Decline(:bias) — additive masks are not taken by the fused kernel")
+    q, k, v = (run.value(i) for i in op.ins[:3])           # ops.jl:1365-1391
+    # the mem-efficient variant's fourth input is the additive mask, (Lk, Lq, H, B) in the graph's order
+    bias = run.value(op.ins[3]) if len(op.ins) > 3 and "efficient" in op.aten else None
+    if bias is not None and not bias.isdense():
+        bias = run.contiguous(op.ins[3] + "#c", bias)
     E, Lq, H, B = q.shape
     scale = float(op.attrs["scale"]) if op.attrs.get("scale") is not None else 1.0 / sqrt(E)
     out = run.tupledest(0, run.tupledtype(0, np.float32 if q.dtype == np.float32 else q.dtype), E, Lq, H, B)
-    sdpa(run.ctx, q, k, v, None, scale, out=out)
+    sdpa(run.ctx, q, k, v, bias, scale, out=out)
     return (out,) + (None,) * 8                             # a 9-tuple of which only element 0 is real
 
 
@@ -283,6 +352,26 @@ def _op_clone(run: _Run, op: Op):
     return out
 
 
+def _op_to_copy(run: _Run, op: Op):
+    x = run.value(op.ins[0])                                # ops.jl:342-358: the declared dtype of the result
+    b = run.graph.buffers.get(op.out)
+    out = run.dest(op.out, b.dtype if b is not None else x.dtype, x.shape)
+    to_copy_(run.ctx, out, run.contiguous(op.ins[0] + "#c", x))
+    return out
+
+
+def _op_maxpool(run: _Run, op: Op):
+    x = run.value(op.ins[0])                                # ops.jl:1329-1343; x is (W, H, C, N)
+    rev = lambda v: tuple(int(t) for t in reversed(v))
+    k = rev(op.attrs["arg1"])
+    s = rev(op.attrs["arg2"]) if op.attrs.get("arg2") else k
+    p = rev(op.attrs["arg3"]) if op.attrs.get("arg3") else (0, 0)
+    W, H, Cn, N = x.shape
+    out = run.tupledest(0, x.dtype, (W + 2 * p[0] - k[0]) // s[0] + 1, (H + 2 * p[1] - k[1]) // s[1] + 1, Cn, N)
+    maxpool2d_(run.ctx, out, x, k, s, p)                    # strided views are read in place
+    return (out, None)                                      # the indices are never read
+
+
 def _op_convolution(run: _Run, op: Op):
     x, w = run.value(op.ins[0]), run.value(op.ins[1])       # ops.jl:1114-1222 (2-D, one group)
     bias = run.value(op.ins[2]) if len(op.ins) >= 3 else None
@@ -306,6 +395,7 @@ RUNOP = {
     "_scaled_dot_product_efficient_attention.default": _op_sdpa,
     "native_layer_norm.default": _op_layernorm, "gelu.default": _op_gelu, "add.Tensor": _op_add,
     "clamp.default": _op_clamp, "clone.default": _op_clone, "convolution.default": _op_convolution,
+    "_to_copy.default": _op_to_copy, "max_pool2d_with_indices.default": _op_maxpool,
 }
 
 

@@ -1,0 +1,82 @@
+"""Graph-level ops around the hot path, run through Model/execute!: _to_copy (and its fold into the
+producer), max_pool2d_with_indices, and the mem-efficient attention op with its additive mask."""
+import numpy as np
+import pytest
+
+import juliavision_b200 as jv
+from juliavision_b200.graph import loadgraph
+
+from .conftest import relerr
+from .test_graph_plan import _castgraph
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n", [1, 7, 8, 1000, 4099, 1 << 20])
+def test_to_copy_is_the_numpy_cast(ctx, n):
+    rng = np.random.default_rng(n)
+    a32 = np.float32(rng.standard_normal(n) * 100)
+    a32[0] = 70000.0                                   # beyond fp16: rounds to inf, as convert does
+    out16 = ctx.allocate(np.float16, n)
+    jv.to_copy_(ctx, out16, ctx.toback(a32))
+    with np.errstate(over="ignore"):
+        assert np.array_equal(out16.to_host(), a32.astype(np.float16))
+    a16 = np.float16(rng.standard_normal(n))
+    out32 = ctx.allocate(np.float32, n)
+    jv.to_copy_(ctx, out32, ctx.toback(a16))
+    assert np.array_equal(out32.to_host(), a16.astype(np.float32))
+
+
+def test_folded_cast_gives_the_same_values(ctx):
+    """foldoutcasts is only allowed to be free: the graph with the narrowing cast folded into the layer
+    norm returns bit-for-bit what the op-by-op graph returns."""
+    rng = np.random.default_rng(1)
+    g = _castgraph()
+    w = {"g": np.float32(1 + 0.1 * rng.standard_normal(16)), "w": np.float16(rng.standard_normal((16, 8)) * 0.2),
+         "b": np.float16(rng.standard_normal(8) * 0.2)}
+    x = np.float32(rng.standard_normal((6, 16)))
+    plain = jv.Model(ctx, g, w, rewrite=False)
+    folded = jv.Model(ctx, g, w, rewrite=True)
+    assert folded.rewrites["foldoutcasts"] == 1 and len(folded.graph.ops) == len(plain.graph.ops) - 1
+    a, b = plain(x), folded(x)
+    ctx.synchronize()
+    for u, v in zip(a, b):
+        assert u.dtype == v.dtype and np.array_equal(u.to_host(), v.to_host())
+    assert a[1].dtype == np.float32                    # the widening cast survived
+
+
+def test_maxpool_and_masked_attention_ops(ctx, ora):
+    """max_pool2d_with_indices (tuple result, element 0) and _scaled_dot_product_efficient_attention
+    with its fourth input, the additive mask, through the op loop."""
+    B, H, L, E = 2, 2, 64, 16
+    g = loadgraph({
+        "name": "ops", "symbols": [], "inputs": ["img", "q", "k", "v", "mask"], "outputs": ["p0", "a0"],
+        "buffers": [
+            {"id": "img", "kind": "external", "shape": [1, 8, 12, 16], "dtype": "float16"},
+            {"id": "q", "kind": "external", "shape": [B, H, L, E], "dtype": "float16"},
+            {"id": "k", "kind": "external", "shape": [B, H, L, E], "dtype": "float16"},
+            {"id": "v", "kind": "external", "shape": [B, H, L, E], "dtype": "float16"},
+            {"id": "mask", "kind": "external", "shape": [B, 1, L, L], "dtype": "float16"},
+            {"id": "p", "kind": "transient", "shape": [], "dtype": "float16", "live": [1, 1],
+             "shapes": [[1, 8, 6, 8], [1, 8, 6, 8]], "dtypes": ["float16", None]},
+            {"id": "p0", "kind": "view", "shape": [1, 8, 6, 8], "dtype": "float16", "of": "p", "op": "getitem", "attrs": {"arg1": 0}},
+            {"id": "a", "kind": "transient", "shape": [], "dtype": "float16", "live": [2, 2],
+             "shapes": [[B, H, L, E], None, None, None], "dtypes": ["float16", None, None, None]},
+            {"id": "a0", "kind": "view", "shape": [B, H, L, E], "dtype": "float16", "of": "a", "op": "getitem", "attrs": {"arg1": 0}},
+        ],
+        "ops": [
+            {"id": "o1", "aten": "max_pool2d_with_indices.default", "in": ["img"], "out": "p", "attrs": {"arg1": [2, 2], "arg2": [2, 2]}},
+            {"id": "o2", "aten": "_scaled_dot_product_efficient_attention.default", "in": ["q", "k", "v", "mask"], "out": "a",
+             "attrs": {"scale": 0.25}},
+        ]})
+    rng = np.random.default_rng(2)
+    img = np.float16(rng.standard_normal((1, 8, 12, 16)))
+    q, k, v = (np.float16(rng.standard_normal((B, H, L, E))) for _ in range(3))
+    mask = np.float16(rng.standard_normal((B, 1, L, L)))
+    mask[rng.random(mask.shape) < 0.25] = -np.inf
+    m = jv.Model(ctx, g, {})
+    p0, a0 = m(img, q, k, v, mask)
+    ctx.synchronize()
+    assert np.array_equal(p0.to_host(), ora.maxpool2d(img, (2, 2), (2, 2)))
+    ref = ora.attention_ref(q, k, v, 0.25, bias=mask)
+    assert relerr(a0.to_host(), ref) < 5e-3

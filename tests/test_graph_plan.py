@@ -4,6 +4,7 @@ the slab stays within 1.6x of the liveness bound, outputs are never planned."""
 import json
 
 import numpy as np
+import pytest
 
 from juliavision_b200.encoder import EncoderConfig, init_weights
 from juliavision_b200.encoder_graph import encoder_graph
@@ -70,3 +71,94 @@ def test_hoistpermutes_and_foldgelu():
     assert len(g.ops) == before - cfg.layers and not any(o.aten == "gelu.default" for o in g.ops)
     assert sum(o.attrs.get("act") == "gelu" for o in g.ops) == cfg.layers
     assert checkslab(g, {}, planslab(g, {}))[1] == 0           # still a valid plan after the rewrites
+
+
+def _write_safetensors(path, tensors, metadata=None):
+    import json
+    import struct
+    names = {np.dtype(np.float16): "F16", np.dtype(np.float32): "F32", np.dtype(np.int64): "I64", np.dtype(np.uint16): "BF16",
+             np.dtype(np.bool_): "BOOL"}
+    header, blobs, off = {}, [], 0
+    if metadata:
+        header["__metadata__"] = metadata
+    for k, v in tensors.items():
+        raw = np.ascontiguousarray(v).tobytes()
+        header[k] = {"dtype": names[v.dtype], "shape": list(v.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    head = json.dumps(header).encode()
+    head += b" " * (-len(head) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(head)))
+        f.write(head)
+        for b in blobs:
+            f.write(b)
+
+
+def test_readsafetensors_round_trip(tmp_path):
+    """safetensors.jl:14-58: header length, JSON header, raw little-endian data; shapes as stored (the
+    upload reverses them), scalars 0-dimensional, bf16 as its bit patterns, metadata skipped."""
+    from juliavision_b200.safetensors import readsafetensors, safetensorsnames
+    rng = np.random.default_rng(0)
+    t = {"enc.w": np.float16(rng.standard_normal((5, 3, 2))), "enc.b": np.float32(rng.standard_normal(7)),
+         "step": np.array(41, dtype=np.int64), "bf": np.arange(6, dtype=np.uint16).reshape(2, 3),
+         "mask": np.array([True, False, True])}
+    path = str(tmp_path / "w.safetensors")
+    _write_safetensors(path, t, metadata={"format": "pt"})
+    assert sorted(safetensorsnames(path)) == sorted(t)
+    got = readsafetensors(path)
+    assert sorted(got) == sorted(t)
+    for k in t:
+        assert got[k].shape == t[k].shape and got[k].dtype == t[k].dtype
+        assert np.array_equal(got[k], t[k])
+    assert got["step"].ndim == 0 and int(got["step"]) == 41
+    with open(path, "r+b") as f:                      # a file cut short is an error, not a short array
+        f.truncate(40)
+    with pytest.raises(ValueError):
+        readsafetensors(path)
+
+
+def _castgraph():
+    """layer norm in fp32 -> getitem -> _to_copy to fp16 -> addmm; plus a widening cast that must stay."""
+    from juliavision_b200.graph import loadgraph
+    return loadgraph({
+        "name": "casts", "symbols": [], "inputs": ["x"], "outputs": ["y", "wide"],
+        "buffers": [
+            {"id": "x", "kind": "external", "shape": [6, 16], "dtype": "float32"},
+            {"id": "g", "kind": "weight", "shape": [16], "dtype": "float32", "key": "g"},
+            {"id": "w", "kind": "weight", "shape": [16, 8], "dtype": "float16", "key": "w"},
+            {"id": "b", "kind": "weight", "shape": [8], "dtype": "float16", "key": "b"},
+            {"id": "ln", "kind": "transient", "shape": [], "dtype": "float32", "live": [1, 2],
+             "shapes": [[6, 16], [6, 1], [6, 1]], "dtypes": ["float32", "float32", "float32"]},
+            {"id": "ln0", "kind": "view", "shape": [6, 16], "dtype": "float32", "of": "ln", "op": "getitem", "attrs": {"arg1": 0}},
+            {"id": "h", "kind": "transient", "shape": [6, 16], "dtype": "float16", "live": [2, 3]},
+            {"id": "y", "kind": "transient", "shape": [6, 8], "dtype": "float16", "live": [3, 4]},
+            {"id": "wide", "kind": "transient", "shape": [6, 8], "dtype": "float32", "live": [4, 4]},
+        ],
+        "ops": [
+            {"id": "o1", "aten": "native_layer_norm.default", "in": ["x", "g", "g"], "out": "ln", "attrs": {"arg1": [16], "arg4": 1e-5}},
+            {"id": "o2", "aten": "_to_copy.default", "in": ["ln0"], "out": "h", "attrs": {}},
+            {"id": "o3", "aten": "addmm.default", "in": ["b", "h", "w"], "out": "y", "attrs": {}},
+            {"id": "o4", "aten": "_to_copy.default", "in": ["y"], "out": "wide", "attrs": {}},
+        ]})
+
+
+def test_foldoutcasts_retypes_the_producer_and_keeps_widening_casts():
+    """foldoutcasts.jl:82-155: the narrowing cast behind the layer norm disappears (its result becomes
+    an alias and the tuple element is declared fp16); the widening cast stays."""
+    from juliavision_b200.execute import foldoutcasts
+    g = _castgraph()
+    assert foldoutcasts(g) == 1
+    assert [o.id for o in g.ops] == ["o1", "o3", "o4"]
+    assert g.buffers["ln"].attrs["dtypes"][0] == np.float16 and g.buffers["ln"].attrs["dtypes"][1] == np.float32
+    assert g.buffers["ln0"].dtype == np.float16
+    h = g.buffers["h"]
+    assert h.kind == "view" and h.of == "ln0" and h.viewop == "alias.default"
+    assert foldoutcasts(g) == 0                      # idempotent
+
+
+def test_foldoutcasts_needs_a_single_reader():
+    from juliavision_b200.execute import foldoutcasts
+    g = _castgraph()
+    g.outputs.append("ln0")                          # someone else reads the wide value
+    assert foldoutcasts(g) == 0
