@@ -210,6 +210,29 @@ def kernel_figures(ctx, jv, pk, quick: bool):
                                        frac_of_measured_hbm=round(byts / ms / 1e6 / pk["hbm_gbs"], 4),
                                        frac_of_spec_8000=round(byts / ms / 1e6 / 8000.0, 4))
 
+    # one-token matrix-vector products (the decoder-side shape): bytes of the weight per second
+    for gm, gk, gdt in ((5120, 1280, np.float32), (51865, 1280, np.float16)):
+        sets = []
+        for _ in range(8):
+            Wd = ctx.toback((rng.standard_normal((gk, gm), dtype=np.float32) * 0.05).astype(gdt))
+            xd = ctx.toback(rng.standard_normal((1, gk), dtype=np.float32).astype(gdt))
+            sets.append((Wd, xd, ctx.allocate(gdt, gm, 1)))
+        it = [0]
+
+        def gv():
+            Wd, xd, od = sets[it[0] % len(sets)]
+            it[0] += 1
+            ctx.ws.reset()
+            jv.matmul_(ctx, od, Wd, xd, None)
+        for _ in range(3):
+            gv()
+        ctx.synchronize()
+        ms = time_region(ctx, gv, 40)
+        byts = gm * gk * np.dtype(gdt).itemsize
+        out[f"gemv_{gm}x{gk}_{np.dtype(gdt).name}"] = dict(ms=round(ms, 5), gbs=round(byts / ms / 1e6, 1),
+                                                            frac_of_measured_hbm=round(byts / ms / 1e6 / pk["hbm_gbs"], 4))
+        del sets
+
     # the whole Hiera-B+-shaped image encoder (1024x1024x3 in, 24 blocks, 32x32x896 out), one image and
     # eight per pass, each pass replayed as a CUDA graph
     from juliavision_b200.hiera import Hiera, HieraConfig

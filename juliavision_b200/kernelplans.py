@@ -36,6 +36,13 @@ class MMScalarPlan:
 
 
 @dataclass(frozen=True)
+class MMGemvPlan:
+    """One column of B — "batch 1" in the reversed layout (mm_gemv_plan, matmul.jl:103-130): the
+    bandwidth-bound matrix-vector kernel.  The reference takes it for fp32 operands only; here fp16
+    operands take it too, since a 128-token tile would be almost empty."""
+
+
+@dataclass(frozen=True)
 class FlashTCPlan:
     """Fused single-pass attention on tcgen05; stands where FlashCMPlan stood
     (kernelplans.jl:54-324). BR/BC are the query/key block, EP the padded head dim."""

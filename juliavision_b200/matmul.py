@@ -13,7 +13,7 @@ import numpy as np
 from . import _lib
 from ._lib import B200Error, check
 from .context import Ctx, DeviceArray, dtcode
-from .kernelplans import Decline, MMScalarPlan, MMTilePlan
+from .kernelplans import Decline, MMGemvPlan, MMScalarPlan, MMTilePlan
 
 
 def _colmajor_2d(a: DeviceArray):
@@ -24,8 +24,29 @@ def _colmajor_2d(a: DeviceArray):
     return ld if ld >= a.shape[0] else None
 
 
+def _gemv_plan(out, A, B, bias):
+    """mm_gemv_plan (matmul.jl:122-130): one column of B, dense operands of one float type, a bias of
+    length M.  None when this is not a matrix-vector product; a Decline only for an odd bias."""
+    if not (A.ndim == B.ndim == out.ndim == 2 and B.shape[1] == 1 and out.shape == (A.shape[0], 1)
+            and B.shape[0] == A.shape[1] and min(A.shape) >= 1):
+        return None
+    if A.dtype != B.dtype or A.dtype not in (np.float16, np.float32):
+        return None
+    if out.dtype != np.float32 and out.dtype != A.dtype:
+        return None
+    if _colmajor_2d(A) is None or not B.isdense() or not out.isdense():
+        return None
+    if bias is not None and (bias.dtype != A.dtype or bias.size != A.shape[0] or not bias.isdense()):
+        return Decline("bias") if A.dtype == np.float32 else None
+    return MMGemvPlan()
+
+
 def mmplan(ctx: Ctx, out: DeviceArray, A: DeviceArray, B: DeviceArray, bias: Optional[DeviceArray] = None):
-    """Which path this shape takes (matmul.jl:91-95,172-179): MMTilePlan, MMScalarPlan or Decline."""
+    """Which path this shape takes (matmul.jl:91-95,103-130,172-179): MMTilePlan, MMGemvPlan,
+    MMScalarPlan or Decline."""
+    g = _gemv_plan(out, A, B, bias)
+    if g is not None:
+        return g
     if A.dtype != np.float16 or B.dtype != np.float16:
         return Decline("operands")
     if out.dtype not in (np.float16, np.float32):
@@ -63,6 +84,10 @@ def matmul_(ctx: Ctx, out: DeviceArray, A: DeviceArray, B: DeviceArray, bias: Op
         raise B200Error(16, f"matmul!: Decline(:{plan.reason}) for A{A.shape}:{A.dtype} B{B.shape}:{B.dtype}")
     M, K = A.shape
     N = B.shape[1]
+    if isinstance(plan, MMGemvPlan):
+        check(_lib.lib().b200_gemv(ctx.handle, M, K, A.ptr, _colmajor_2d(A), B.ptr, bias.ptr if bias is not None else None,
+                                   dtcode(A.dtype), out.ptr, dtcode(out.dtype), _lib.EPI[epi]))
+        return out
     check(_lib.lib().b200_gemm_f16(ctx.handle, M, N, K, A.ptr, _colmajor_2d(A), B.ptr, _colmajor_2d(B),
                                    bias.ptr if bias is not None else None, out.ptr, _colmajor_2d(out),
                                    dtcode(out.dtype), _lib.EPI[epi], 1, 0, 0, 0))

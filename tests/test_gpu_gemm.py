@@ -38,7 +38,7 @@ def test_vs_oracle(ctx, ora, tokens, out, K):
     rng = np.random.default_rng(tokens * 7 + out * 3 + K)
     X, Wt, b = _case(rng, tokens, out, K, scale=0.25)
     plan = jv.mmplan(ctx, ctx.allocate(np.float16, out, tokens), ctx.toback(Wt), ctx.toback(X))
-    assert isinstance(plan, jv.MMTilePlan), plan
+    assert isinstance(plan, jv.MMGemvPlan if tokens == 1 else jv.MMTilePlan), plan
     for epi, bias in (("identity", b), ("gelu", b), ("relu", None)):
         got = linear_gpu(ctx, X, Wt, bias, epi=epi)
         ref = ora.linear(X, Wt, bias, epi=epi if epi != "identity" else "none")
@@ -182,3 +182,31 @@ def test_sweep_rows_sampled_and_row_shards(ctx, ora, tokens, out, K):
             part = linear_gpu(ctx, np.ascontiguousarray(X[r0:r1]), Wt, b)
             assert relerr(part, got[r0:r1]) < 1e-3
             assert np.mean(part != got[r0:r1]) < 1e-3      # summation order may differ where a tile was split along K
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("M,K", [(1280, 1280), (5120, 1280), (1280, 5120), (51865, 1280), (37, 50), (8, 4096), (1000, 3)])
+def test_gemv_one_token(ctx, ora, dtype, M, K):
+    """The one-token case (MMGemvPlan, matmul.jl:103-137): fp32 operands as in the reference and fp16
+    ones; bias and activation in the store; compared with the oracle's fp32-accumulated product."""
+    rng = np.random.default_rng(M + K)
+    Wt = (rng.standard_normal((K, M)) * 0.05).astype(dtype)          # torch (in, out): column-major (M, K)
+    x = (rng.standard_normal((1, K))).astype(dtype)
+    b = (rng.standard_normal(M) * 0.05).astype(dtype)
+    A, B, bias = ctx.toback(Wt), ctx.toback(x), ctx.toback(b)
+    for epi, bb in (("identity", bias), ("gelu", bias), ("relu", None)):
+        out = ctx.allocate(dtype, M, 1)
+        ctx.fill_bytes(out, 0xFF)
+        assert isinstance(jv.mmplan(ctx, out, A, B, bb), jv.MMGemvPlan)
+        ctx.ws.reset()
+        jv.matmul_(ctx, out, A, B, bb, epi=epi)
+        ctx.synchronize()
+        got = out.to_host()
+        want = x.astype(np.float64) @ Wt.astype(np.float64) + (b.astype(np.float64) if bb is not None else 0)
+        if dtype == np.float16:
+            ref = ora.linear(x, Wt, b if bb is not None else None, epi=epi if epi != "identity" else "none")
+            assert relerr(got, ref) < TOL, describe(got, ref, TOL)
+        else:
+            from scipy.special import erf
+            ref = {"identity": want, "relu": np.maximum(want, 0), "gelu": 0.5 * want * (1 + erf(want / np.sqrt(2)))}[epi]
+            assert relerr(got, ref) < 1e-4, describe(got, ref, 1e-4)
