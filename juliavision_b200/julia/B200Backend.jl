@@ -181,8 +181,14 @@ struct Strided4
 end
 s4(a) = (r = rootstrides(a); Strided4(Ptr{Cvoid}(r[1]), Int64.(r[2])))
 
+# An additive mask does not decline here: the fused kernel adds it (b200_attention_f16_bias).  It must
+# be Float16 and broadcast to (Lk, Lq, H, B), the graph's own order (attention.jl:55-59).
 function sdpaplan(ctx::Ctx{B200Backend}, q, k, v, bias)
-    bias === nothing || return (Decline(:bias), k, v)
+    if bias !== nothing
+        eltype(bias) === Float16 || return (Decline(:eltype), k, v)
+        all(i -> size(bias, i) in (1, (size(k, 2), size(q, 2), size(q, 3), size(q, 4))[i]), 1:4) ||
+            return (Decline(:bias), k, v)
+    end
     all(x -> eltype(x) === Float16, (q, k, v)) || return (Decline(:eltype), k, v)
     any(x -> rootstrides(x) === nothing, (q, k, v)) && return (Decline(:wrapped), k, v)
     E, Lq, H, B = size(q); Lk = size(k, 2)
@@ -198,11 +204,23 @@ end
 function sdpa!(ctx, ::Union{FlashTCPlan,AttnScalarPlan}, out, q, k, v, bias, scale)
     E, Lq, H, B = size(q); Lk = size(k, 2)
     out === nothing && (out = KernelAbstractions.allocate(ctx.backend, accum(eltype(q)), E, Lq, H, B))
-    check(ccall((:b200_attention_f16, LIB), Cint,
-                (Ptr{Cvoid}, Int64, Int64, Int64, Int64, Int64, Ref{Strided4}, Ref{Strided4}, Ref{Strided4},
-                 Ptr{Cvoid}, Cint, Cfloat),
-                ctx.backend.handle, E, Lq, Lk, H, B, s4(q), s4(k), s4(v), pointer(out), dtcode(eltype(out)),
-                Float32(scale)))
+    # `out` may be any (E, Lq, H, B) view with E contiguous: a token-major destination folds the
+    # clone that follows sdpa in the exported graphs into the store.
+    if bias === nothing
+        check(ccall((:b200_attention_f16_strided, LIB), Cint,
+                    (Ptr{Cvoid}, Int64, Int64, Int64, Int64, Int64, Ref{Strided4}, Ref{Strided4}, Ref{Strided4},
+                     Ref{Strided4}, Cint, Cfloat),
+                    ctx.backend.handle, E, Lq, Lk, H, B, s4(q), s4(k), s4(v), s4(out), dtcode(eltype(out)),
+                    Float32(scale)))
+    else
+        b = s4(bias)   # a size-1 axis broadcasts: stride 0
+        b = Strided4(b.ptr, ntuple(i -> size(bias, i) == 1 ? Int64(0) : b.stride[i], 4))
+        check(ccall((:b200_attention_f16_bias, LIB), Cint,
+                    (Ptr{Cvoid}, Int64, Int64, Int64, Int64, Int64, Ref{Strided4}, Ref{Strided4}, Ref{Strided4},
+                     Ref{Strided4}, Ref{Strided4}, Cint, Cfloat),
+                    ctx.backend.handle, E, Lq, Lk, H, B, s4(q), s4(k), s4(v), b, s4(out), dtcode(eltype(out)),
+                    Float32(scale)))
+    end
     out
 end
 
@@ -217,6 +235,66 @@ function layernorm!(ctx::Ctx{B200Backend}, out, mean, rstd, a, γ, β, C::Intege
                 β === nothing ? C_NULL : pointer(β), Float32(eps)))
     out
 end
+
+# x .= clamp.(x .+ h); layernorm!(out, mean, rstd, x, ...) in one launch: the target of a load-time
+# rewrite that folds add.Tensor (+ clamp.default) into the native_layer_norm that follows.
+function addlayernorm!(ctx::Ctx{B200Backend}, out, mean, rstd, x, h, γ, β, C::Integer, eps::Real; clamp = nothing)
+    lo, hi = clamp === nothing ? (0f0, 0f0) : Float32.(clamp)
+    check(ccall((:b200_add_layernorm_f16, LIB), Cint,
+                (Ptr{Cvoid}, Int64, Int64, Ptr{Cvoid}, Ptr{Cvoid}, Cint, Cfloat, Cfloat, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
+                 Ptr{Cvoid}, Ptr{Cvoid}, Cfloat),
+                ctx.backend.handle, length(x) ÷ C, C, pointer(x), pointer(h), clamp === nothing ? 0 : 1, lo, hi,
+                pointer(out), pointer(mean), pointer(rstd), γ === nothing ? C_NULL : pointer(γ),
+                β === nothing ? C_NULL : pointer(β), Float32(eps)))
+    out
+end
+
+# ------------------------------------------------------------------ matmul!(::MMGemvPlan) (matmul.jl:103-137)
+function mm_gemv_plan(dev::B200Caps, out, A, B, bias)
+    T = eltype(A)
+    (T === Float32 || T === Float16) && eltype(B) === T || return Decline(:operands)
+    size(B, 2) == 1 || return Decline(:notvector)
+    bias === nothing || (bias isa AbstractVector && length(bias) == size(A, 1)) || return Decline(:bias)
+    MMGemvPlan()
+end
+function matmul!(ctx::Ctx{B200Backend}, ::MMGemvPlan, out, A, B, bias, epi; gemm = NamedTuple())
+    M, K = size(A)
+    check(ccall((:b200_gemv, LIB), Cint,
+                (Ptr{Cvoid}, Int64, Int64, Ptr{Cvoid}, Int64, Ptr{Cvoid}, Ptr{Cvoid}, Cint, Ptr{Cvoid}, Cint, Cint),
+                ctx.backend.handle, M, K, pointer(A), stride(A, 2), pointer(B),
+                bias === nothing ? C_NULL : pointer(bias), dtcode(eltype(A)), pointer(out), dtcode(eltype(out)),
+                epicode(epi)))
+    out
+end
+
+# ------------------------------------------------------------------ maxpool2d!, _to_copy (resample.jl:141, ops.jl:342-358)
+function maxpool2d!(ctx::Ctx{B200Backend}, out, x, k, s, p)
+    xs, os = rootstrides(x), rootstrides(out)     # any (x, y, c, n) view: the NCHW permutes need no copy
+    W, H, C, N = size(x)
+    check(ccall((:b200_maxpool2d_f16, LIB), Cint,
+                (Ptr{Cvoid}, Int64, Int64, Int64, Int64, Ptr{Cvoid}, Ptr{Int64}, Ptr{Cvoid}, Ptr{Int64}, Int64, Int64, Int64,
+                 Int64, Int64, Int64),
+                ctx.backend.handle, W, H, C, N, Ptr{Cvoid}(xs[1]), collect(Int64.(xs[2])), Ptr{Cvoid}(os[1]),
+                collect(Int64.(os[2])), k[1], k[2], s[1], s[2], p[1], p[2]))
+    out
+end
+function tocopy!(ctx::Ctx{B200Backend}, out, a)
+    check(ccall((:b200_cast, LIB), Cint, (Ptr{Cvoid}, Ptr{Cvoid}, Cint, Ptr{Cvoid}, Cint, Int64),
+                ctx.backend.handle, pointer(a), dtcode(eltype(a)), pointer(out), dtcode(eltype(out)), length(a)))
+    out
+end
+
+# ------------------------------------------------------------------ capture / replay! (SAM2Runner/src/sam2.jl:90-115)
+# Run the ops once (sizes the pool and the workspace), then record them; replay! launches the graph.
+function capture(f, b::B200Backend)
+    f(); KernelAbstractions.synchronize(b)
+    check(ccall((:b200_graph_begin, LIB), Cint, (Ptr{Cvoid},), b.handle))
+    f()
+    g = Ref{Ptr{Cvoid}}(C_NULL)
+    check(ccall((:b200_graph_end, LIB), Cint, (Ptr{Cvoid}, Ref{Ptr{Cvoid}}), b.handle, g))
+    g[]
+end
+replay!(b::B200Backend, g::Ptr{Cvoid}) = check(ccall((:b200_graph_launch, LIB), Cint, (Ptr{Cvoid}, Ptr{Cvoid}), b.handle, g))
 
 # ------------------------------------------------------------------ convolution! (conv.jl:100-145)
 function convolution!(ctx::Ctx{B200Backend}, out, x, w, bias, stride, padding, dilation, groups; act = :none)
