@@ -111,8 +111,10 @@ def kernel_figures(ctx, jv, pk, quick: bool):
     """Per-kernel throughput on the other BASELINE configs, each timed alone with CUDA events on
     inputs that rotate through more than L2's worth of buffers."""
     import ctypes as C
+    from juliavision_b200 import _lib
     out = {}
     rng = np.random.default_rng(7)
+    ctx_sms = jv.caps(ctx).cores
 
     def gemm_case(tokens, feats, K, epi="identity", bias=True, nbuf=None):
         per = (tokens * K + K * feats + tokens * feats) * 2
@@ -137,8 +139,25 @@ def kernel_figures(ctx, jv, pk, quick: bool):
         reps = 20 if quick else 50
         ms = time_region(ctx, go, reps)
         tf = 2.0 * tokens * feats * K / ms / 1e9
-        return dict(ms=round(ms, 5), tflops=round(tf, 1), frac_of_measured_peak=round(tf / pk["tflops"], 4),
-                    frac_of_spec_2250=round(tf / 2250.0, 4), buffers=nbuf)
+        res = dict(ms=round(ms, 5), tflops=round(tf, 1), frac_of_measured_peak=round(tf / pk["tflops"], 4),
+                   frac_of_spec_2250=round(tf / 2250.0, 4), buffers=nbuf)
+        # One more launch, straight after the timed ones, with the library's timeline on: the first
+        # tile's main loop of worker 0 in nanoseconds and in SM cycles gives the clock the SM really ran
+        # at (the part is power-capped under this load) and the cycles per 64-deep k-block, of which
+        # 512 would be the tensor pipe's own time for a 256x256 tile (8192 flop/clk/SM).
+        tl = ctx.allocate(np.uint64, 256)
+        ctx.fill_bytes(tl, 0)
+        _lib.check(_lib.lib().b200_timeline(ctx.handle, tl.ptr))
+        go()
+        ctx.synchronize()
+        _lib.check(_lib.lib().b200_timeline(ctx.handle, None))
+        t = tl.to_host().astype(np.int64)
+        ns, clk, nkb = int(t[4] - t[3]), int(t[64 + 4] - t[64 + 3]), (K + 63) // 64
+        if ns > 0 and clk > 0:
+            mhz = clk / ns * 1e3
+            res.update(sm_mhz_in_main_loop=round(mhz), clk_per_kblock=round(clk / nkb, 1),
+                       frac_of_tensor_peak_at_that_clock=round(tf / (ctx_sms * 8192 * mhz * 1e6 / 1e12), 4))
+        return res
 
     out["gemm_config1_4096x3072x768"] = gemm_case(4096, 3072, 768)
     out["gemm_4096x4096x4096"] = gemm_case(4096, 4096, 4096, bias=False)

@@ -149,6 +149,13 @@ int b200_gemm_f16_plan(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t n
 int b200_gemv(b200_ctx* ctx, int64_t M, int64_t K, const void* A, int64_t lda, const void* x,
               const void* bias, int in_dtype, void* out, int out_dtype, int epilogue);
 
+/* Diagnostics: while dptr (a device buffer of 256 uint64, zeroed by the caller) is set, worker 0 of
+ * every GEMM launch records a timeline into it — globaltimer nanoseconds at [slot] and the SM's cycle
+ * counter at [64 + slot]; slots: 0 entry, 1 set-up done, 3 first operand stage landed, 4.. all UMMAs
+ * of the worker's tile 0, 1, 2, 3+ issued, 8.. their accumulators complete, 12.. their epilogues
+ * done, 16 exit.  NULL stops it.  bench.py reads the SM clock inside the main loop from it. */
+int b200_timeline(b200_ctx* ctx, void* dptr);
+
 /* -------------------------------------------------------------------- attention */
 /*
  * Fused non-causal scaled-dot-product attention, single pass, online softmax.

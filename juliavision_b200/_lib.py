@@ -75,6 +75,7 @@ SIGNATURES = {
                              _i64, _i64]),
     "b200_gemm_f16_supported": (_i32, [_i64, _i64, _i64, _i64, _i64, _i64, _i32]),
     "b200_gemm_f16_plan": (_i32, [_vp, _i64, _i64, _i64, _i64, C.POINTER(GemmPlan)]),
+    "b200_timeline": (_i32, [_vp, _vp]),
     "b200_gemv": (_i32, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _i32, _vp, _i32, _i32]),
     "b200_attention_f16": (_i32, [_vp, _i64, _i64, _i64, _i64, _i64, C.POINTER(Strided4), C.POINTER(Strided4),
                                   C.POINTER(Strided4), _vp, _i32, _f32]),

@@ -363,10 +363,8 @@ int b200_workspace_stats(b200_ctx* c, size_t* used, size_t* cap, int* retired) {
     return B200_OK;
 }
 
-// Development aid, not part of the public header: point the GEMM timeline at a device buffer of
-// at least 32 uint64 slots (or null to stop).
-int b200_internal_gemm_trace(b200_ctx* c, void* dptr) {
-    B200_REQUIRE(c, B200_EINVAL, "gemm_trace: null ctx");
+int b200_timeline(b200_ctx* c, void* dptr) {
+    B200_REQUIRE(c, B200_EINVAL, "timeline: null ctx");
     c->gemm_trace = static_cast<unsigned long long*>(dptr);
     return B200_OK;
 }

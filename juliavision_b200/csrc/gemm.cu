@@ -72,11 +72,15 @@ template <typename OutT> struct GemmParams {
     unsigned long long* trace;  // optional timeline of worker 0 (globaltimer ns), null in normal use
 };
 
-// Timeline slots written by worker 0 when tracing: a development aid for reading where a launch
-// spends its time; costs one predictable branch per event otherwise.
+// Timeline slots written by worker 0 when tracing (b200_timeline): globaltimer ns at [slot] and
+// the SM's own cycle counter at [64 + slot], so a phase can be read both in time and in cycles (their
+// ratio is the clock the SM actually ran at).  Costs one predictable branch per event otherwise.
 #define GEMM_TRACE(slot)                                                   \
     do {                                                                   \
-        if (p.trace != nullptr && worker == 0 && rank == 0) p.trace[(slot)] = globaltimer_ns(); \
+        if (p.trace != nullptr && worker == 0 && rank == 0) {              \
+            p.trace[(slot)] = globaltimer_ns();                            \
+            p.trace[64 + (slot)] = (unsigned long long)clock64();          \
+        }                                                                  \
     } while (0)
 
 __device__ __forceinline__ float erf_as(float x) {

@@ -55,7 +55,25 @@ gemv_kernel(const T* __restrict__ A, int64_t lda, const T* __restrict__ x, const
 #pragma unroll
     for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
     if (m0 < M) {
-        for (int64_t k = k0 + warp; k < k1; k += GEMV_WARPS) {
+        // Four columns of A in flight per lane: the loop is otherwise one load deep and latency-bound.
+        constexpr int UN = 4;
+        int64_t k = k0 + warp;
+        for (; k + (UN - 1) * GEMV_WARPS < k1; k += UN * GEMV_WARPS) {
+            T a[UN][VEC];
+            float xv[UN];
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const T* col = A + (k + u * GEMV_WARPS) * lda + m0;
+                if constexpr (VEC > 1) *reinterpret_cast<uint4*>(a[u]) = __ldg(reinterpret_cast<const uint4*>(col));
+                else a[u][0] = col[0];
+                xv[u] = gemv_tof<T>(x[k + u * GEMV_WARPS]);
+            }
+#pragma unroll
+            for (int u = 0; u < UN; ++u)
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) acc[v] = fmaf(gemv_tof<T>(a[u][v]), xv[u], acc[v]);
+        }
+        for (; k < k1; k += GEMV_WARPS) {
             const float xv = gemv_tof<T>(x[k]);
             const T* col = A + k * lda + m0;
             if constexpr (VEC > 1) {
@@ -106,10 +124,10 @@ static int gemv_run(b200_ctx* ctx, int64_t M, int64_t K, const void* A, int64_t 
     const bool vec = lda % VECMAX == 0 && (reinterpret_cast<uintptr_t>(A) & 15u) == 0;
     const int rows_per_block = 32 * (vec ? VECMAX : 1);
     const int64_t mblocks = cdiv(M, rows_per_block);
-    // Enough blocks to keep every SM's memory pipe busy, but at least 64 k-steps per warp each.
-    const int64_t want = (int64_t)ctx->prop.multiProcessorCount * 4;
+    // Enough blocks to keep every SM's memory pipe busy, but at least 16 k-steps per warp each.
+    const int64_t want = (int64_t)ctx->prop.multiProcessorCount * 6;
     int64_t ksplit = mblocks >= want ? 1 : cdiv(want, mblocks);
-    const int64_t maxsplit = K / (64 * GEMV_WARPS) > 0 ? K / (64 * GEMV_WARPS) : 1;
+    const int64_t maxsplit = K / (16 * GEMV_WARPS) > 0 ? K / (16 * GEMV_WARPS) : 1;
     if (ksplit > maxsplit) ksplit = maxsplit;
     if (ksplit > 64) ksplit = 64;
     const int64_t kchunk = cdiv(K, ksplit);
