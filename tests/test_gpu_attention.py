@@ -167,3 +167,37 @@ def test_config2_sample_rows_vs_oracle(ctx, ora):
     rows = np.sort(rng.choice(L, 64, replace=False))
     ref = ora.attention_ref(np.ascontiguousarray(q[:, :, rows]), k, v, 0.125)
     assert relerr(got[:, :, rows], ref) < TOL, describe(got[:, :, rows], ref, TOL)
+
+
+@pytest.mark.parametrize("B,H,Lq,Lk,E", [(512, 2, 64, 64, 56), (1024, 4, 16, 64, 56), (300, 2, 64, 64, 64), (256, 2, 49, 49, 32)])
+def test_many_small_windows_packed(ctx, ora, B, H, Lq, Lk, E):
+    """Attention windows of a few dozen tokens, token-major with the windows back to back (what the image
+    encoder hands over): the library runs several windows as one sequence under a block-diagonal mask.
+    Values must be those of independent windows: checked against the oracle window by window, and a
+    window's result must not change when its neighbours do."""
+    from .gpu_helpers import qkv_views
+    rng = np.random.default_rng(B + Lq + Lk)
+    qb = np.float16(rng.standard_normal((B, Lq, H, E)))
+    kb = np.float16(rng.standard_normal((B, Lk, H, E)))
+    vb = np.float16(rng.standard_normal((B, Lk, H, E)))
+    q, k, v = (t.transpose(0, 2, 1, 3) for t in (qb, kb, vb))            # torch (B,H,L,E) views
+    scale = 1 / np.sqrt(E)
+
+    def run(q, k, v):
+        dq, dk, dv = qkv_views(ctx, q, k, v)
+        buf = ctx.allocate(np.float16, E * H, Lq, B)                      # torch (B, Lq, H*E)
+        ctx.fill_bytes(buf, 0xFF)
+        view = jv.DeviceArray(ctx, buf.ptr, np.float16, (E, Lq, H, B), (1, E * H, E, E * H * Lq), owner=buf)
+        jv.sdpa(ctx, dq, dk, dv, None, scale, out=view)
+        ctx.synchronize()
+        return buf.to_host().reshape(B, Lq, H, E).transpose(0, 2, 1, 3)
+
+    got = run(q, k, v)
+    ref = ora.attention_ref(q, k, v, scale)
+    assert np.all(np.isfinite(got))
+    assert relerr(got, ref) < TOL, describe(got, ref, TOL)
+    kb2, vb2 = kb.copy(), vb.copy()
+    kb2[1::2] = np.float16(rng.standard_normal(kb2[1::2].shape) * 3)       # disturb every other window
+    vb2[1::2] = 7
+    got2 = run(q, kb2.transpose(0, 2, 1, 3), vb2.transpose(0, 2, 1, 3))
+    assert np.array_equal(got2[0::2], got[0::2])
