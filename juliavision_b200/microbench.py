@@ -3,6 +3,7 @@
     python -m juliavision_b200.microbench gemm --tokens 4096 --features 4096 --k 4096 [--epi gelu] [--reps 20]
     python -m juliavision_b200.microbench attention --batch 1 --heads 12 --seq 4096 --head-dim 64
     python -m juliavision_b200.microbench layernorm --groups 65536 --channels 1280
+    python -m juliavision_b200.microbench hiera --batch 1          # whole image-encoder pass, eager launches
 
 Each run warms up, then times `reps` back-to-back calls over `--buffers` rotating operand sets
 (so L2 does not keep one set resident) and prints one JSON line.  With `--reps` small this is also
@@ -82,6 +83,17 @@ def layernorm(ctx, a):
     return dict(op="layernorm", groups=a.groups, channels=a.channels, ms=round(ms, 5), gbs=round(nbytes / ms / 1e6, 1))
 
 
+def hiera(ctx, a):
+    from .hiera import Hiera, HieraConfig
+    cfg = HieraConfig()
+    m = Hiera(ctx, cfg, batch=a.batch)
+    rng = np.random.default_rng(a.seed)
+    ctx.upload(m.image, np.float16(rng.random((a.batch, cfg.in_ch, cfg.image, cfg.image), dtype=np.float32)))
+    ms = _time(ctx, m.forward, a.reps, warmup=2)
+    return dict(op="hiera", batch=a.batch, ms_per_img=round(ms / a.batch, 4), tflops=round(cfg.flops(a.batch) / ms / 1e9, 1),
+                launches_per_pass=m.launches_per_pass())
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="op", required=True)
@@ -99,14 +111,16 @@ def main():
     ln = sub.add_parser("layernorm")
     ln.add_argument("--groups", type=int, default=65536)
     ln.add_argument("--channels", type=int, default=1280)
-    for s in (g, at, ln):
+    hi = sub.add_parser("hiera")
+    hi.add_argument("--batch", type=int, default=1)
+    for s in (g, at, ln, hi):
         s.add_argument("--reps", type=int, default=20)
         s.add_argument("--buffers", type=int, default=3)
         s.add_argument("--seed", type=int, default=0)
         s.add_argument("--device", type=int, default=0)
     a = ap.parse_args()
     with jv.Ctx(a.device) as ctx:
-        print(json.dumps({"gemm": gemm, "attention": attention, "layernorm": layernorm}[a.op](ctx, a)), flush=True)
+        print(json.dumps({"gemm": gemm, "attention": attention, "layernorm": layernorm, "hiera": hiera}[a.op](ctx, a)), flush=True)
 
 
 if __name__ == "__main__":
