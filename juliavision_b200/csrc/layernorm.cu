@@ -64,8 +64,18 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// One warp per group; lane l owns vectors l, l+32, ... (VPL of them at most).
-template <typename InT, typename OutT, int VPL>
+// Sum over the LPG lanes of a group (LPG a power of two; the butterfly never leaves the aligned span).
+template <int LPG>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+    for (int o = LPG / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// One warp per group; lane l owns vectors l, l+32, ... (VPL of them at most).  Narrow groups (at most
+// 16 or 8 vectors, VPL = 1) share a warp, LPG lanes each, so that no lane idles; the sums are the same
+// butterflies with the empty upper steps left out, hence the same bits.
+template <typename InT, typename OutT, int VPL, int LPG = 32>
 __global__ void __launch_bounds__(128)
 ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restrict__ mean,
                float* __restrict__ rstd, const InT* __restrict__ gamma,
@@ -73,10 +83,10 @@ ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restr
     constexpr int VN = Vec16<InT>::N;
     grid_dep_wait();     // the input is the previous kernel's output
     grid_dep_launch();
-    const int lane = threadIdx.x & 31;
-    const int64_t g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (g >= groups) return;
-    const int nvec = C / VN;
+    static_assert(LPG == 32 || VPL == 1, "only single-vector groups share a warp");
+    const int lane = threadIdx.x & (LPG - 1);
+    const int64_t g = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPG;
+    const int nvec = g < groups ? C / VN : 0;   // lanes past the last group idle through the shuffles
     const InT* src = a + g * (int64_t)C;
 
     float x[VPL][VN];
@@ -93,7 +103,7 @@ ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restr
         }
     }
     const float n = (float)C;
-    const float mu = warp_sum(s) / n;
+    const float mu = group_sum<LPG>(s) / n;
     float s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
@@ -105,7 +115,7 @@ ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restr
             }
         }
     }
-    const float r = 1.0f / sqrtf(warp_sum(s2) / n + eps);
+    const float r = 1.0f / sqrtf(group_sum<LPG>(s2) / n + eps);
 
     OutT* dst = out + g * (int64_t)C;
 #pragma unroll
@@ -134,7 +144,7 @@ ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restr
             store_vec<VN>(dst + (int64_t)v * VN, y);
         }
     }
-    if (lane == 0) {
+    if (lane == 0 && g < groups) {
         mean[g] = mu;
         rstd[g] = r;
     }
@@ -145,7 +155,7 @@ ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restr
 // Bit-identical to running add.Tensor, clamp.default and native_layer_norm one after another
 // (each rounds to fp16 where the separate ops would), but x and h are read once and the three
 // launches become one.
-template <int VPL>
+template <int VPL, int LPG = 32>
 __global__ void __launch_bounds__(128)
 ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half* __restrict__ out,
                    float* __restrict__ mean, float* __restrict__ rstd, const __half* __restrict__ gamma,
@@ -154,10 +164,10 @@ ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half*
     constexpr int VN = 8;
     grid_dep_wait();     // x and h are the previous kernels' outputs
     grid_dep_launch();
-    const int lane = threadIdx.x & 31;
-    const int64_t g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (g >= groups) return;
-    const int nvec = C / VN;
+    static_assert(LPG == 32 || VPL == 1, "only single-vector groups share a warp");
+    const int lane = threadIdx.x & (LPG - 1);
+    const int64_t g = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPG;
+    const int nvec = g < groups ? C / VN : 0;
     __half* xr = x + g * (int64_t)C;
     const __half* hr = h + g * (int64_t)C;
 
@@ -184,7 +194,7 @@ ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half*
         }
     }
     const float n = (float)C;
-    const float mu = warp_sum(s) / n;
+    const float mu = group_sum<LPG>(s) / n;
     float s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i)
@@ -195,7 +205,7 @@ ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half*
                 s2 += d * d;
             }
         }
-    const float r = 1.0f / sqrtf(warp_sum(s2) / n + eps);
+    const float r = 1.0f / sqrtf(group_sum<LPG>(s2) / n + eps);
     __half* dst = out + g * (int64_t)C;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
@@ -223,7 +233,7 @@ ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half*
             store_vec<VN>(dst + (int64_t)vi * VN, y);
         }
     }
-    if (lane == 0) {
+    if (lane == 0 && g < groups) {
         mean[g] = mu;
         rstd[g] = r;
     }
@@ -298,7 +308,12 @@ static int launch_ln(b200_ctx* ctx, int64_t groups, int64_t C, const void* a, vo
 #define LN_GO(V)                                                                                            \
     B200_CUDA(launch_dep(ln_warp_kernel<InT, OutT, V>, grid, block, 0, ctx->stream, 1, ap, op, mean, rstd, gp, bp, \
                          groups, (int)C, eps))
-        if (vpl <= 1) LN_GO(1);
+#define LN_GO_SHARED(L)                                                                                     \
+    B200_CUDA(launch_dep(ln_warp_kernel<InT, OutT, 1, L>, dim3((unsigned)cdiv(groups, wpb * (32 / L))), block, 0,   \
+                         ctx->stream, 1, ap, op, mean, rstd, gp, bp, groups, (int)C, eps))
+        if (nvec <= 8) LN_GO_SHARED(8);
+        else if (nvec <= 16) LN_GO_SHARED(16);
+        else if (vpl <= 1) LN_GO(1);
         else if (vpl <= 2) LN_GO(2);
         else if (vpl <= 3) LN_GO(3);
         else if (vpl <= 4) LN_GO(4);
@@ -308,6 +323,7 @@ static int launch_ln(b200_ctx* ctx, int64_t groups, int64_t C, const void* a, vo
         else if (vpl <= 12) LN_GO(12);
         else LN_GO(16);
 #undef LN_GO
+#undef LN_GO_SHARED
     } else {
         ln_block_kernel<InT, OutT><<<(unsigned)groups, 256, 0, ctx->stream>>>(ap, op, mean, rstd, gp, bp,
                                                                              C, eps);
@@ -347,7 +363,13 @@ extern "C" int b200_add_layernorm_f16(b200_ctx* ctx, int64_t groups, int64_t C, 
     B200_CUDA(launch_dep(ln_add_warp_kernel<V>, grid, block, 0, ctx->stream, 1, (__half*)x, (const __half*)h,           \
                          (__half*)out, mean, rstd, (const __half*)gamma, (const __half*)beta, groups, (int)C, eps, \
                          use_clamp, lo, hi))
-    if (vpl <= 1) LNA_GO(1);
+#define LNA_GO_SHARED(L)                                                                                          \
+    B200_CUDA(launch_dep(ln_add_warp_kernel<1, L>, dim3((unsigned)cdiv(groups, wpb * (32 / L))), block, 0, ctx->stream, 1, \
+                         (__half*)x, (const __half*)h, (__half*)out, mean, rstd, (const __half*)gamma,             \
+                         (const __half*)beta, groups, (int)C, eps, use_clamp, lo, hi))
+    if (nvec <= 8) LNA_GO_SHARED(8);
+    else if (nvec <= 16) LNA_GO_SHARED(16);
+    else if (vpl <= 1) LNA_GO(1);
     else if (vpl <= 2) LNA_GO(2);
     else if (vpl <= 3) LNA_GO(3);
     else if (vpl <= 4) LNA_GO(4);
@@ -357,6 +379,7 @@ extern "C" int b200_add_layernorm_f16(b200_ctx* ctx, int64_t groups, int64_t C, 
     else if (vpl <= 12) LNA_GO(12);
     else LNA_GO(16);
 #undef LNA_GO
+#undef LNA_GO_SHARED
     ctx->launches++;
     B200_CUDA(cudaGetLastError());
     return B200_OK;

@@ -18,7 +18,7 @@ def test_golden(ctx):
 
 
 @pytest.mark.parametrize("groups,C", [(1500, 1280), (4096, 112), (64, 144), (333, 576), (7, 100), (5, 4104),
-                                      (3, 8200), (1, 8), (65536, 112)])
+                                      (3, 8200), (1, 8), (65536, 112), (999, 112), (1001, 64), (7, 56), (130, 128)])
 @pytest.mark.parametrize("dt_in,dt_out", [(np.float16, np.float16), (np.float16, np.float32),
                                           (np.float32, np.float32), (np.float32, np.float16)])
 def test_vs_oracle(ctx, ora, groups, C, dt_in, dt_out):
