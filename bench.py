@@ -291,7 +291,7 @@ def run_reference(args):
         return
     from juliavision_b200.encoder import EncoderConfig, init_weights
     cfg = EncoderConfig()
-    layers = 1
+    layers = 4
     weights = init_weights(EncoderConfig(layers=layers)) + []
     x = np.float16(np.random.default_rng(11).standard_normal((cfg.tokens, cfg.d_model), dtype=np.float32))
     from oracle import oracle as ora
@@ -325,7 +325,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="encoder depth (32 = the named config)")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel figures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
-    ap.add_argument("--cpu-layers", type=int, default=2)
+    ap.add_argument("--cpu-layers", type=int, default=10, help="layers of the CPU baseline sample (about 1 s each on 16 cores)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
