@@ -62,6 +62,12 @@ struct AttnParams {
     // Several short sequences packed into one (set by the host when windows are small): query i may
     // only see the keys of its own window, i / dq == key / dk.  0 = no packing.
     int dq, dk;
+    // Keys split over nsplit CTAs per query pair (few queries, many keys): each writes its unnormalised
+    // fp32 O rows to part_o[split][b][h][lq][E] and (reference point, row sum) to part_ml[...][2];
+    // attention_merge_kernel combines them (the reference's attn_flash_cm_merge!, flash.jl:1398-1421).
+    int nsplit;
+    float* part_o;
+    float* part_ml;
 };
 
 #define ATT_TRACE(slot)                                                                              \
@@ -133,11 +139,18 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
         half = (item - p.pair_ctas) & 1;
         item = p.pair_ctas + ((item - p.pair_ctas) >> 1);
     }
+    int split = 0;
+    if (p.nsplit > 1) {
+        split = item % p.nsplit;
+        item /= p.nsplit;
+    }
     const int qp = item % p.qpairs;
     const int h = (item / p.qpairs) % p.H;
     const int b = item / (p.qpairs * p.H);
     const int q0 = qp * (2 * ATT_BR) + (half > 0 ? ATT_BR : 0);
-    const int nblk = (p.Lk + ATT_BC - 1) / ATT_BC;
+    const int nblk_all = (p.Lk + ATT_BC - 1) / ATT_BC;
+    const int jb0 = p.nsplit > 1 ? (int)((int64_t)split * nblk_all / p.nsplit) : 0;           // first key block of this CTA
+    const int nblk = (p.nsplit > 1 ? (int)((int64_t)(split + 1) * nblk_all / p.nsplit) : nblk_all) - jb0;
     const int ntiles = (half < 0 && q0 + ATT_BR < p.Lq) ? 2 : 1;   // the second tile may lie wholly past Lq
 
     if (threadIdx.x == 0) {
@@ -192,10 +205,10 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 const uint32_t ph = (uint32_t)((j / ATT_KV_STAGES) & 1);
                 if (!mbar_wait(&k_empty[s], ph ^ 1, p.d_status, KST_WAIT_EMPTY, abort_flag)) break;
                 mbar_arrive_expect_tx(&k_full[s], ATT_TILE_BYTES);
-                tma_load_4d(tile_ptr(ATT_T_K + s), &tmapK, &k_full[s], 0, j * ATT_BC, h, b);
+                tma_load_4d(tile_ptr(ATT_T_K + s), &tmapK, &k_full[s], 0, (jb0 + j) * ATT_BC, h, b);
                 if (!mbar_wait(&v_empty[s], ph ^ 1, p.d_status, KST_WAIT_EMPTY, abort_flag)) break;
                 mbar_arrive_expect_tx(&v_full[s], ATT_TILE_BYTES);
-                tma_load_4d(tile_ptr(ATT_T_V + s), &tmapV, &v_full[s], 0, j * ATT_BC, h, b);
+                tma_load_4d(tile_ptr(ATT_T_V + s), &tmapV, &v_full[s], 0, (jb0 + j) * ATT_BC, h, b);
             }
         }
     } else if (warp == 9 || warp == 10) {
@@ -281,7 +294,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
             for (int j = 0; ok && j < nblk; ++j) {
                 if (!mbar_wait(&s_full[t], (uint32_t)(j & 1), p.d_status, KST_WAIT_TMEM_FULL, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const int nvalid = p.Lk - j * ATT_BC; // keys of this block that exist (>= 128 when full)
+                const int nvalid = p.Lk - (jb0 + j) * ATT_BC; // keys of this block that exist (>= 128 when full)
                 if (lane == 0 && quad == 0 && j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 2);  // S(0, j) ready
 
                 // The whole row of S (128 fp32) comes into registers in one round trip; S is then
@@ -307,7 +320,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                             for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__uint_as_float(r[c][i]) * sc);
                     } else {
                         const __half* brow = p.bias + (int64_t)(lq < p.Lq ? lq : 0) * p.bsQ + (int64_t)h * p.bsH +
-                                             (int64_t)b * p.bsB + (int64_t)j * ATT_BC * p.bsK;
+                                             (int64_t)b * p.bsB + (int64_t)(jb0 + j) * ATT_BC * p.bsK;
                         if (p.bias_vec && nvalid >= ATT_BC) {
 #pragma unroll
                             for (int c = 0; c < 4; ++c)
@@ -334,7 +347,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                     }
                     if (p.dq > 0) {
                         // packed windows: only the keys [lo, hi) of this block belong to this row's window
-                        const int lo = (lq / p.dq) * p.dk - j * ATT_BC, hi = lo + p.dk;
+                        const int lo = (lq / p.dq) * p.dk - (jb0 + j) * ATT_BC, hi = lo + p.dk;
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -442,6 +455,31 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
             if (ok) {
                 tc_fence_after();
                 const int lq = q0 + t * ATT_BR + row;
+                if (p.nsplit > 1) {
+                    // Unnormalised rows and their (reference point, sum) for the merge.  tcgen05.ld is a
+                    // warp-wide (.sync.aligned) instruction: every lane executes it, whether or not its
+                    // row exists; only the stores are predicated.
+                    const int64_t prow = (((int64_t)split * p.B + b) * p.H + h) * p.Lq + (lq < p.Lq ? lq : 0);
+                    float* po = p.part_o + prow * p.E;
+#pragma unroll 1
+                    for (int c = 0; c < ATT_EP / 32; ++c) {
+                        uint32_t r[32];
+                        tmem_ld32(o_tmem + c * 32, r);
+                        tmem_wait_ld();
+                        if (lq < p.Lq) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4)
+                                if (c * 32 + i < p.E)
+                                    *reinterpret_cast<float4*>(po + c * 32 + i) =
+                                        make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                                                    __uint_as_float(r[i + 3]));
+                        }
+                    }
+                    if (lq < p.Lq) {
+                        p.part_ml[prow * 2] = m_run;
+                        p.part_ml[prow * 2 + 1] = l_run;
+                    }
+                } else {
                 const float inv = 1.0f / (l_run == 0.f ? 1.0f : l_run);
                 const int64_t obase = lq * p.osL + h * p.osH + b * p.osB;
 #pragma unroll 1
@@ -476,6 +514,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                         }
                     }
                 }
+                }   // nsplit == 1
             }
         }
     }
@@ -488,6 +527,41 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
     if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem_base, ATT_TMEM_COLS);
+    }
+}
+
+// Combine the partial results of a key split (attn_flash_cm_merge!, flash.jl:1398-1421): one warp per
+// query row; out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M the largest reference point.
+__global__ void __launch_bounds__(128)
+attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nsplit, int E, int Lq, int H,
+                       int B, void* out, int64_t osL, int64_t osH, int64_t osB, int out_f32) {
+    grid_dep_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t rows = (int64_t)Lq * H * B;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lq = (int)(row % Lq), h = (int)((row / Lq) % H), b = (int)(row / ((int64_t)Lq * H));
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(s * rows + row) * 2]);
+    float den = 0.f, num0 = 0.f, num1 = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float m = part_ml[(s * rows + row) * 2], l = part_ml[(s * rows + row) * 2 + 1];
+        const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+        den = fmaf(l, w, den);
+        const float* po = part_o + (s * rows + row) * E;
+        if (lane < E) num0 = fmaf(po[lane], w, num0);
+        if (lane + 32 < E) num1 = fmaf(po[lane + 32], w, num1);
+    }
+    const float inv = 1.0f / (den == 0.f ? 1.0f : den);
+    const int64_t obase = lq * osL + h * osH + b * osB;
+    if (out_f32) {
+        float* o = static_cast<float*>(out) + obase;
+        if (lane < E) o[lane] = num0 * inv;
+        if (lane + 32 < E) o[lane + 32] = num1 * inv;
+    } else {
+        __half* o = static_cast<__half*>(out) + obase;
+        if (lane < E) o[lane] = __float2half_rn(num0 * inv);
+        if (lane + 32 < E) o[lane + 32] = __float2half_rn(num1 * inv);
     }
 }
 
@@ -709,6 +783,36 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
     const int64_t pairs = (int64_t)p.qpairs * H * B;
     B200_REQUIRE(pairs < (1ll << 30), B200_DECLINE_EXTENT, "attention: too many query tiles");
     const int64_t sms = ctx->prop.multiProcessorCount;
+    // Few queries over many keys (a decode step: Lq = 23, Lk = 4096) would leave most SMs idle: split
+    // the keys over several CTAs per query pair, at least two key blocks each, and merge.
+    p.nsplit = 1;
+    p.part_o = p.part_ml = nullptr;
+    const int64_t nblk_all = cdiv(Lk, ATT_BC);
+    if (bptr == nullptr && pack_dq == 0 && 2 * pairs <= sms && nblk_all >= 4) {
+        int64_t ns = sms / pairs;
+        if (ns > nblk_all / 2) ns = nblk_all / 2;
+        if (ns > 64) ns = 64;
+        if (ns >= 2) {
+            const int64_t rows = Lq * H * B;
+            void* ws = nullptr;
+            rc = ws_scratch(ctx, (size_t)(ns * rows * (E + 2)) * sizeof(float), &ws);
+            if (rc) return rc;
+            p.nsplit = (int)ns;
+            p.part_o = static_cast<float*>(ws);
+            p.part_ml = p.part_o + ns * rows * E;
+        }
+    }
+    if (p.nsplit > 1) {
+        p.pair_ctas = (int)(pairs * p.nsplit);
+        B200_CUDA(launch_dep(attention_f16_tc_kernel<false>, dim3((unsigned)(pairs * p.nsplit), 1, 1), dim3(ATT_THREADS, 1, 1),
+                             ATT_SMEM_BYTES, ctx->stream, 1, tq, tk, tv, p));
+        const int64_t rows = Lq * H * B;
+        B200_CUDA(launch_dep(attention_merge_kernel, dim3((unsigned)cdiv(rows, 4), 1, 1), dim3(128, 1, 1), 0, ctx->stream, 1,
+                             (const float*)p.part_o, (const float*)p.part_ml, p.nsplit, (int)E, (int)Lq, (int)H, (int)B, out,
+                             o->stride[1], o->stride[2], o->stride[3], (int)(out_dtype == B200_F32)));
+        ctx->launches += 2;
+        return B200_OK;
+    }
     const int64_t rem = pairs % sms;
     // Split the pairs of a last wave that would leave more than half of the SMs idle — but not a
     // pair whose second tile does not exist.

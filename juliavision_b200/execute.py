@@ -7,7 +7,8 @@ its rewrite passes: `hoistpermutes` (hoistcasts.jl:62-112 — a `t`/`permute` vi
 dense weight, which is what puts `addmm` on the tensor-core path) and the gelu half of `foldrelu`
 (foldrelu.jl:81-124 — `gelu(addmm(...))` becomes `addmm` with `attrs["act"] = "gelu"`), and
 `foldoutcasts` (foldoutcasts.jl:82-155 — a narrowing cast folded into the declared dtype of the layer
-norm or clone that feeds it).
+norm or clone that feeds it) and `foldincasts` (foldincasts.jl:82-124 — a widening cast in front of a
+layer norm dropped, the layer norm reading the fp16 value).
 An op outside this set raises, as `runop!`'s fallback does (execute.jl:541-542).
 """
 from __future__ import annotations
@@ -147,6 +148,46 @@ def foldoutcasts(graph: Graph) -> int:
     return n
 
 
+WIDECAST_READERS = ("native_layer_norm.default",)
+
+
+def foldincasts(graph: Graph) -> int:
+    """A `_to_copy` that widens fp16 to fp32 in front of a layer norm, read by nothing else: the layer
+    norm reads the fp16 value directly (foldincasts.jl:82-124).  fp16 -> fp32 is exact and the layer norm
+    accumulates in fp32 for either input, so it sees the same values (here the fp16 and fp32 kernels deal
+    elements to lanes differently, so a sum may differ in its last bit); its result keeps the dtype the
+    graph declares for it.  Readers are counted through views."""
+    readers: Dict[str, List[Op]] = {}
+    for o in graph.ops:
+        for i in o.ins:
+            readers.setdefault(_viewchain(graph, i)[-1], []).append(o)
+    isoutput = {_viewchain(graph, o)[-1] for o in graph.outputs}
+    drop, n = set(), 0
+    for cast in graph.ops:
+        if cast.aten != "_to_copy.default" or len(cast.ins) != 1:
+            continue
+        ob, ib = graph.buffers.get(cast.out), graph.buffers.get(cast.ins[0])
+        if ob is None or ib is None or ob.kind != "transient" or list(ob.shape) != list(ib.shape):
+            continue
+        if not (np.dtype(ib.dtype) == np.float16 and np.dtype(ob.dtype) in (np.dtype(np.float32), np.dtype(np.float64))):
+            continue
+        rs = readers.get(cast.out, [])
+        if cast.out in isoutput or len(rs) != 1 or rs[0].aten not in WIDECAST_READERS:
+            continue
+        # This runtime's layer norm reads gamma and beta in its input's dtype: fold only when they are
+        # fp16 already (or absent); wide ones would have to be rounded, which the fold must never do.
+        wb = [graph.buffers.get(i) for i in rs[0].ins[1:3]]
+        if any(b is None or np.dtype(b.dtype) != np.float16 for b in wb):
+            continue
+        graph.buffers[cast.out] = Buffer(cast.out, "view", list(ib.shape), ib.dtype, of=cast.ins[0], viewop="alias.default",
+                                         attrs=dict(ob.attrs))
+        drop.add(cast.id)
+        n += 1
+    if n:
+        graph.ops[:] = [o for o in graph.ops if o.id not in drop]
+    return n
+
+
 # ------------------------------------------------------------------------------ model
 class Model:
     """Model(graph, weights): rewrite, upload, plan (driver.jl:128-182). `weights` maps safetensors
@@ -157,11 +198,12 @@ class Model:
         self.ctx, self.dims = ctx, dims or {}
         self.graph = copy.deepcopy(graph)
         weights = dict(weights)
-        self.rewrites = dict(hoistpermutes=0, foldgelu=0, foldoutcasts=0)
+        self.rewrites = dict(hoistpermutes=0, foldgelu=0, foldoutcasts=0, foldincasts=0)
         if rewrite:
             self.rewrites["hoistpermutes"] = hoistpermutes(self.graph, weights)
             self.rewrites["foldgelu"] = foldgelu(self.graph)
             self.rewrites["foldoutcasts"] = foldoutcasts(self.graph)
+            self.rewrites["foldincasts"] = foldincasts(self.graph)
         self.weights: Dict[str, DeviceArray] = {}
         for b in self.graph.buffers.values():
             if b.kind == "weight":
@@ -309,6 +351,10 @@ def _op_layernorm(run: _Run, op: Op):
     g = run.value(op.ins[1]) if len(op.ins) >= 2 else None
     b = run.value(op.ins[2]) if len(op.ins) >= 3 else None
     a = run.contiguous(op.ins[0] + "#c", a)
+    # gamma/beta narrower than the input are widened (exact) into scratch; the kernel reads them in the input's dtype
+    widen = lambda t: t if t is None or t.dtype == a.dtype or np.dtype(t.dtype).itemsize > a.dtype.itemsize \
+        else to_copy_(run.ctx, run.ctx.scratch(a.dtype, *t.shape), t)
+    g, b = widen(g), widen(b)
     out = run.tupledest(0, run.tupledtype(0, a.dtype), *a.shape)
     groups = a.size // n
     mean, rstd = run.tupledest(1, np.float32, groups), run.tupledest(2, np.float32, groups)

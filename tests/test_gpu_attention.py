@@ -201,3 +201,20 @@ def test_many_small_windows_packed(ctx, ora, B, H, Lq, Lk, E):
     vb2[1::2] = 7
     got2 = run(q, kb2.transpose(0, 2, 1, 3), vb2.transpose(0, 2, 1, 3))
     assert np.array_equal(got2[0::2], got[0::2])
+
+
+@pytest.mark.parametrize("B,H,Lq,Lk,E", [(1, 8, 23, 4096, 64), (2, 3, 1, 4000, 56), (1, 1, 300, 2048, 32), (1, 20, 130, 1500, 64)])
+def test_few_queries_many_keys_split_and_merged(ctx, ora, B, H, Lq, Lk, E):
+    """Decode-like shapes (flash.jl:298-323: Lq = 23, Lk = 4096): the keys are split over several CTAs
+    per query tile and merged (attn_flash_cm_merge!); the values are those of the unsplit computation."""
+    rng = np.random.default_rng(Lq + Lk + E)
+    q = np.float16(rng.standard_normal((B, H, Lq, E)))
+    k = np.float16(rng.standard_normal((B, H, Lk, E)))
+    v = np.float16(rng.standard_normal((B, H, Lk, E)))
+    k[:, :, Lk // 2] *= 4          # a late key that moves the running maximum of some rows
+    scale = 1 / np.sqrt(E)
+    ref = ora.attention_ref(q, k, v, scale)
+    for out_dtype in (np.float16, np.float32):
+        got, plan = attention_gpu(ctx, q, k, v, scale, out_dtype)
+        assert isinstance(plan, jv.FlashTCPlan)
+        assert relerr(got, ref) < TOL, describe(got, ref, TOL)

@@ -98,7 +98,7 @@ def test_exported_graph_through_execute_equals_direct_calls(ctx):
     g, wts = encoder_graph(cfg, w)
     graph = loadgraph(json.loads(json.dumps(g)))
     model = Model(ctx, graph, wts)
-    assert model.rewrites == dict(hoistpermutes=6 * cfg.layers, foldgelu=cfg.layers, foldoutcasts=0)
+    assert model.rewrites == dict(hoistpermutes=6 * cfg.layers, foldgelu=cfg.layers, foldoutcasts=0, foldincasts=0)
     (out,) = model(x.reshape(1, cfg.tokens, cfg.d_model))
     ctx.synchronize()
     got = out.to_host().reshape(cfg.tokens, cfg.d_model)

@@ -80,3 +80,21 @@ def test_maxpool_and_masked_attention_ops(ctx, ora):
     assert np.array_equal(p0.to_host(), ora.maxpool2d(img, (2, 2), (2, 2)))
     ref = ora.attention_ref(q, k, v, 0.25, bias=mask)
     assert relerr(a0.to_host(), ref) < 5e-3
+
+
+def test_folded_widening_cast_gives_the_same_values(ctx):
+    """foldincasts: the layer norm reading fp16 directly sees the same values (fp16 -> fp32 is exact) and
+    accumulates in fp32 as before; its fp16 and fp32 kernels deal elements to lanes differently, so the
+    sums may differ in the last bit and nothing more."""
+    from .test_graph_plan import _widegraph
+    rng = np.random.default_rng(3)
+    g = _widegraph()
+    w = {"g": np.float16(1 + 0.1 * rng.standard_normal(16))}
+    a, b = (np.float16(rng.standard_normal((6, 16))) for _ in range(2))
+    plain, folded = jv.Model(ctx, g, w, rewrite=False), jv.Model(ctx, g, w, rewrite=True)
+    assert folded.rewrites["foldincasts"] == 1
+    u, v = plain(a, b), folded(a, b)
+    ctx.synchronize()
+    for x, y in zip(u, v):
+        assert x.dtype == y.dtype == np.float32
+        assert np.max(np.abs(x.to_host() - y.to_host())) <= 4e-7 * max(1.0, float(np.max(np.abs(x.to_host()))))

@@ -162,3 +162,43 @@ def test_foldoutcasts_needs_a_single_reader():
     g = _castgraph()
     g.outputs.append("ln0")                          # someone else reads the wide value
     assert foldoutcasts(g) == 0
+
+
+def _widegraph():
+    """add in fp16 -> _to_copy to fp32 -> layer norm declared fp32; plus a widening cast read by an addmm."""
+    from juliavision_b200.graph import loadgraph
+    return loadgraph({
+        "name": "widen", "symbols": [], "inputs": ["a", "b"], "outputs": ["ln0", "y"],
+        "buffers": [
+            {"id": "a", "kind": "external", "shape": [6, 16], "dtype": "float16"},
+            {"id": "b", "kind": "external", "shape": [6, 16], "dtype": "float16"},
+            {"id": "g", "kind": "weight", "shape": [16], "dtype": "float16", "key": "g"},
+            {"id": "s", "kind": "transient", "shape": [6, 16], "dtype": "float16", "live": [1, 3]},
+            {"id": "w32", "kind": "transient", "shape": [6, 16], "dtype": "float32", "live": [2, 3]},
+            {"id": "ln", "kind": "transient", "shape": [], "dtype": "float32", "live": [3, 3],
+             "shapes": [[6, 16], [6, 1], [6, 1]], "dtypes": ["float32", "float32", "float32"]},
+            {"id": "ln0", "kind": "view", "shape": [6, 16], "dtype": "float32", "of": "ln", "op": "getitem", "attrs": {"arg1": 0}},
+            {"id": "y", "kind": "transient", "shape": [6, 16], "dtype": "float32", "live": [4, 4]},
+        ],
+        "ops": [
+            {"id": "o1", "aten": "add.Tensor", "in": ["a", "b"], "out": "s", "attrs": {}},
+            {"id": "o2", "aten": "_to_copy.default", "in": ["s"], "out": "w32", "attrs": {}},
+            {"id": "o3", "aten": "native_layer_norm.default", "in": ["w32", "g", "g"], "out": "ln", "attrs": {"arg1": [16], "arg4": 1e-5}},
+            {"id": "o4", "aten": "_to_copy.default", "in": ["s"], "out": "y", "attrs": {}},
+        ]})
+
+
+def test_foldincasts_drops_the_widening_cast_in_front_of_a_layer_norm():
+    """foldincasts.jl:82-124: the cast feeding the layer norm becomes an fp16 alias; a widening cast that
+    is a graph output stays."""
+    from juliavision_b200.execute import foldincasts
+    g = _widegraph()
+    assert foldincasts(g) == 1
+    assert [o.id for o in g.ops] == ["o1", "o3", "o4"]
+    w = g.buffers["w32"]
+    assert w.kind == "view" and w.of == "s" and w.dtype == np.float16
+    assert g.buffers["ln"].attrs["dtypes"][0] == np.float32       # the result keeps its declared dtype
+    assert foldincasts(g) == 0
+    wide = _widegraph()
+    wide.buffers["g"].dtype = np.float32          # wide gamma: folding would force a rounding, so it is left alone
+    assert foldincasts(wide) == 0
