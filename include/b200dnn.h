@@ -153,7 +153,8 @@ int b200_gemv(b200_ctx* ctx, int64_t M, int64_t K, const void* A, int64_t lda, c
  * every GEMM launch records a timeline into it — globaltimer nanoseconds at [slot] and the SM's cycle
  * counter at [64 + slot]; slots: 0 entry, 1 set-up done, 3 first operand stage landed, 4.. all UMMAs
  * of the worker's tile 0, 1, 2, 3+ issued, 8.. their accumulators complete, 12.. their epilogues
- * done, 16 exit.  NULL stops it.  bench.py reads the SM clock inside the main loop from it. */
+ * done, 16 exit; [128 + w] is the time worker w (w < 120) left.  NULL stops it.  bench.py reads the SM
+ * clock inside the main loop from it. */
 int b200_timeline(b200_ctx* ctx, void* dptr);
 
 /* -------------------------------------------------------------------- attention */

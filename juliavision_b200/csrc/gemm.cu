@@ -231,11 +231,11 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
     else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const int64_t tiles_per_batch = (int64_t)p.tiles_m * p.tiles_n;
     // Everything above overlapped the previous kernel's tail; from here on its results are needed.
     grid_dep_wait();
     grid_dep_launch();
 
-    const int64_t tiles_per_batch = (int64_t)p.tiles_m * p.tiles_n;
     if (threadIdx.x == 0) GEMM_TRACE(1); // setup done
 
     if (warp == 0) {
@@ -566,6 +566,8 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
     if (threadIdx.x == 0) GEMM_TRACE(16); // exit
+    if (threadIdx.x == 0 && rank == 0 && p.trace != nullptr && worker < 120)
+        p.trace[128 + worker] = globaltimer_ns();   // when each worker left, to see how evenly the work was dealt
 }
 
 // Scalar path for operands the tensor maps cannot express (unaligned pointers or leading
