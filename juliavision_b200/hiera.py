@@ -195,14 +195,20 @@ class Hiera:
         self._to_windows(x, spare, d0, S0, cfg.windows[0])
         add_(ctx, self._view(x, d0 * S0 * S0 * B), self._view(x, d0 * S0 * S0 * B), self.pos.reshape(d0 * S0 * S0 * B))
         cur_w = cfg.windows[0]
-        for b, w in zip(self.plan, self.blocks):
+        pending = False        # the MLP output of the previous block still to be added to the stream (in self.tmp)
+        for i, (b, w) in enumerate(zip(self.plan, self.blocks)):
             ctx.ws.reset()
-            x, spare, cur_w = self._block(b, w, x, spare, cur_w)
+            # the residual add that ends a block is folded into the next block's first layer norm, unless
+            # the tokens are re-ordered in between (after a pooling block) or there is no next block
+            defer = i + 1 < len(self.plan) and not (b["pool"] and cfg.windows[b["stage"]] != cur_w // 2)
+            x, spare, cur_w = self._block(b, w, x, spare, cur_w, pending, defer)
+            pending = defer
         last = self.plan[-1]
         self._to_raster(self.y, x, last["dim"], last["side"], cur_w)
         return self.y
 
-    def _block(self, b: dict, w: Dict[str, DeviceArray], x: DeviceArray, spare: DeviceArray, cur_w: int):
+    def _block(self, b: dict, w: Dict[str, DeviceArray], x: DeviceArray, spare: DeviceArray, cur_w: int,
+               pending: bool = False, defer: bool = False):
         ctx, cfg, B = self.ctx, self.cfg, self.batch
         d_in, d, H, E = b["dim_in"], b["dim"], b["heads"], cfg.head_dim
         T_in, T = b["side_in"] ** 2 * B, b["side"] ** 2 * B
@@ -214,7 +220,10 @@ class Hiera:
         h = self._view(self.h, d_in, T_in)
         mean, rstd = DeviceArray(ctx, self.mean.ptr, np.float32, (T_in,), owner=self.mean), \
             DeviceArray(ctx, self.rstd.ptr, np.float32, (T_in,), owner=self.rstd)
-        layernorm_(ctx, h, mean, rstd, xv, w["ln1_g"], w["ln1_b"], d_in, cfg.eps)
+        if pending:      # x += (previous block's MLP output); h = LN1(x)
+            add_layernorm_(ctx, h, mean, rstd, xv, self._view(self.tmp, d_in, T_in), w["ln1_g"], w["ln1_b"], d_in, cfg.eps)
+        else:
+            layernorm_(ctx, h, mean, rstd, xv, w["ln1_g"], w["ln1_b"], d_in, cfg.eps)
         qkv = self._view(self.qkv, 3 * d, T_in)
         matmul_(ctx, qkv, w["wqkv"], h, w["bqkv"])
         part = lambda i: DeviceArray(ctx, qkv.ptr + i * d * 2, np.float16, (E, Lk, H, nwin), (1, 3 * d, E, 3 * d * Lk), owner=qkv)
@@ -250,7 +259,8 @@ class Hiera:
         ff = self._view(self.ff, d * cfg.mlp_ratio, T)
         matmul_(ctx, ff, w["w1"], h2, w["b1"], epi="gelu")
         matmul_(ctx, o, w["w2"], ff, w["b2"])
-        add_(ctx, self._view(x_new, d * T), self._view(x_new, d * T), self._view(self.tmp, d * T))
+        if not defer:
+            add_(ctx, self._view(x_new, d * T), self._view(x_new, d * T), self._view(self.tmp, d * T))
         new_w = cur_w
         if b["pool"]:
             # tokens now sit in the left stage's windows at half the side; move to this stage's windows
