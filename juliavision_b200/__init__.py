@@ -15,6 +15,7 @@ from .graph import Buffer, Graph, Op, evalshape, loadgraph
 from .kernelplans import AttnScalarPlan, Decline, FlashTCPlan, MMGemvPlan, MMScalarPlan, MMTilePlan
 from .layernorm import add_layernorm_, layernorm_, native_layer_norm
 from .matmul import batchedmatmul_, matmul_, mmplan
+from .rewrites import foldbatchnorm, foldrelu, hoistcasts, weightsource
 from .safetensors import readsafetensors, safetensorsnames
 from .plan import Slab, alignup, checkslab, lifetimes, place, planslab
 from .shard import gather_shards, shard_range, shard_range_py
@@ -25,5 +26,5 @@ __all__ = [
     "FlashTCPlan", "MMScalarPlan", "MMTilePlan", "layernorm_", "add_layernorm_", "native_layer_norm", "batchedmatmul_", "matmul_",
     "mmplan", "Model", "execute_", "hoistpermutes", "foldgelu", "Buffer", "Graph", "Op", "evalshape", "loadgraph",
     "Slab", "alignup", "checkslab", "lifetimes", "place", "planslab", "shard_range", "shard_range_py", "gather_shards",
-    "maxpool2d_", "to_copy_", "MMGemvPlan", "foldoutcasts", "foldincasts", "readsafetensors", "safetensorsnames",
+    "maxpool2d_", "to_copy_", "MMGemvPlan", "foldoutcasts", "foldincasts", "foldbatchnorm", "foldrelu", "hoistcasts", "weightsource", "readsafetensors", "safetensorsnames",
 ]

@@ -200,6 +200,10 @@ class Model:
         weights = dict(weights)
         self.rewrites = dict(hoistpermutes=0, foldgelu=0, foldoutcasts=0, foldincasts=0)
         if rewrite:
+            from .rewrites import foldbatchnorm, foldrelu, hoistcasts
+            extra = dict(hoistcasts=hoistcasts(self.graph, weights), foldbatchnorm=foldbatchnorm(self.graph, weights),
+                         foldrelu=foldrelu(self.graph))
+            self.rewrites.update({k: v for k, v in extra.items() if v})     # listed only when they fired
             self.rewrites["hoistpermutes"] = hoistpermutes(self.graph, weights)
             self.rewrites["foldgelu"] = foldgelu(self.graph)
             self.rewrites["foldoutcasts"] = foldoutcasts(self.graph)
@@ -376,6 +380,8 @@ def _op_add(run: _Run, op: Op):
         raise B200Error(17, f"add.Tensor: broadcasting {a.shape} + {b.shape} is outside the hot path")
     out = run.alloc(op.out, *a.shape)
     add_(run.ctx, out, run.contiguous(op.ins[0] + "#c", a), run.contiguous(op.ins[1] + "#c", b))
+    if _act_name(op.attrs) != "identity":      # a relu folded into the add that ends a residual block (foldrelu)
+        act_(run.ctx, out, out, _act_name(op.attrs))
     return out
 
 

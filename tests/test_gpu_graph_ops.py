@@ -98,3 +98,23 @@ def test_folded_widening_cast_gives_the_same_values(ctx):
     for x, y in zip(u, v):
         assert x.dtype == y.dtype == np.float32
         assert np.max(np.abs(x.to_host() - y.to_host())) <= 4e-7 * max(1.0, float(np.max(np.abs(x.to_host()))))
+
+
+def test_conv_bn_relu_graph_runs_as_one_convolution(ctx, ora):
+    """hoistcasts + foldbatchnorm + foldrelu leave a single convolution whose GEMM store carries the bias
+    and the relu; there is no batch-norm kernel here, so the graph only runs folded."""
+    from .test_graph_plan import _convnet_graph
+    rng = np.random.default_rng(4)
+    w = {"conv.weight": np.float32(rng.standard_normal((4, 3, 3, 3)) * 0.2), "conv.bias": np.float16(rng.standard_normal(4) * 0.1),
+         "bn.weight": np.float32(1 + 0.2 * rng.standard_normal(4)), "bn.bias": np.float32(0.1 * rng.standard_normal(4)),
+         "bn.mean": np.float32(0.1 * rng.standard_normal(4)), "bn.var": np.float32(0.5 + rng.random(4))}
+    x = np.float16(rng.standard_normal((2, 3, 8, 8)))
+    m = jv.Model(ctx, _convnet_graph(), w)
+    assert m.rewrites["foldbatchnorm"] == 1 and m.rewrites["foldrelu"] == 1 and m.rewrites["hoistcasts"] == 1
+    assert [o.aten for o in m.graph.ops] == ["convolution.default"]
+    (y,) = m(x)
+    ctx.synchronize()
+    c = ora.conv2d(x, w["conv.weight"].astype(np.float16), w["conv.bias"], padding=(1, 1)).astype(np.float32)
+    s = w["bn.weight"] / np.sqrt(w["bn.var"] + np.float32(1e-5))
+    want = np.maximum(c * s[None, :, None, None] + (w["bn.bias"] - w["bn.mean"] * s)[None, :, None, None], 0)
+    assert relerr(y.to_host(), want) < 2e-2

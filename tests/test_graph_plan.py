@@ -202,3 +202,59 @@ def test_foldincasts_drops_the_widening_cast_in_front_of_a_layer_norm():
     wide = _widegraph()
     wide.buffers["g"].dtype = np.float32          # wide gamma: folding would force a rounding, so it is left alone
     assert foldincasts(wide) == 0
+
+
+def _convnet_graph():
+    """x -> convolution(w32 cast to fp16, bias) -> batch norm -> getitem 0 -> relu -> y"""
+    from juliavision_b200.graph import loadgraph
+    return loadgraph({
+        "name": "convnet", "symbols": [], "inputs": ["x"], "outputs": ["y"],
+        "buffers": [
+            {"id": "x", "kind": "external", "shape": [2, 3, 8, 8], "dtype": "float16"},
+            {"id": "w32", "kind": "weight", "shape": [4, 3, 3, 3], "dtype": "float32", "key": "conv.weight"},
+            {"id": "w16", "kind": "transient", "shape": [4, 3, 3, 3], "dtype": "float16", "live": [1, 2]},
+            {"id": "cb", "kind": "weight", "shape": [4], "dtype": "float16", "key": "conv.bias"},
+            {"id": "g", "kind": "weight", "shape": [4], "dtype": "float32", "key": "bn.weight"},
+            {"id": "b", "kind": "weight", "shape": [4], "dtype": "float32", "key": "bn.bias"},
+            {"id": "m", "kind": "weight", "shape": [4], "dtype": "float32", "key": "bn.mean"},
+            {"id": "v", "kind": "weight", "shape": [4], "dtype": "float32", "key": "bn.var"},
+            {"id": "c", "kind": "transient", "shape": [2, 4, 8, 8], "dtype": "float16", "live": [2, 3]},
+            {"id": "bn", "kind": "transient", "shape": [], "dtype": "float16", "live": [3, 4],
+             "shapes": [[2, 4, 8, 8], [0], [0]], "dtypes": ["float16", "float32", "float32"]},
+            {"id": "bn0", "kind": "view", "shape": [2, 4, 8, 8], "dtype": "float16", "of": "bn", "op": "getitem", "attrs": {"arg1": 0}},
+            {"id": "y", "kind": "transient", "shape": [2, 4, 8, 8], "dtype": "float16", "live": [4, 4]},
+        ],
+        "ops": [
+            {"id": "cast", "aten": "_to_copy.default", "in": ["w32"], "out": "w16", "attrs": {}},
+            {"id": "conv", "aten": "convolution.default", "in": ["x", "w16", "cb"], "out": "c",
+             "attrs": {"arg3": [1, 1], "arg4": [1, 1], "arg5": [1, 1], "arg6": False, "arg8": 1}},
+            {"id": "bnop", "aten": "_native_batch_norm_legit_no_training.default", "in": ["c", "g", "b", "m", "v"], "out": "bn",
+             "attrs": {"arg5": 0.1, "arg6": 1e-5}},
+            {"id": "relu", "aten": "relu.default", "in": ["bn0"], "out": "y", "attrs": {}},
+        ]})
+
+
+def test_hoistcasts_foldbatchnorm_foldrelu_leave_one_convolution(ora):
+    """hoistcasts.jl:185-226, foldbn.jl:44-143, foldrelu.jl:35-132 on conv -> bn -> relu: one convolution with
+    a scaled weight, a folded bias and the relu in its store; the values match the op-by-op computation."""
+    from juliavision_b200.rewrites import foldbatchnorm, foldrelu, hoistcasts
+    rng = np.random.default_rng(0)
+    w = {"conv.weight": np.float32(rng.standard_normal((4, 3, 3, 3)) * 0.2), "conv.bias": np.float16(rng.standard_normal(4) * 0.1),
+         "bn.weight": np.float32(1 + 0.2 * rng.standard_normal(4)), "bn.bias": np.float32(0.1 * rng.standard_normal(4)),
+         "bn.mean": np.float32(0.1 * rng.standard_normal(4)), "bn.var": np.float32(0.5 + rng.random(4))}
+    g = _convnet_graph()
+    assert hoistcasts(g, w) == 1 and g.buffers["w16"].kind == "weight" and w[g.buffers["w16"].key].dtype == np.float16
+    assert foldbatchnorm(g, w) == 1
+    assert foldrelu(g) == 1
+    assert [o.aten for o in g.ops] == ["convolution.default"] and g.ops[0].attrs["act"] == "relu"
+    assert g.buffers["y"].viewop == "alias.default" and g.buffers["bn0"].of == "c"
+    wk, bk = g.buffers[g.ops[0].ins[1]].key, g.buffers[g.ops[0].ins[2]].key
+    assert w[wk].dtype == np.float16 and w[bk].dtype == np.float16
+    # values: folded convolution == relu(bn(conv(x))) up to the fp16 roundings the unfolded chain makes
+    x = np.float16(rng.standard_normal((2, 3, 8, 8)))
+    folded = ora.conv2d(x, w[wk], w[bk], padding=(1, 1), epi="relu").astype(np.float32)
+    c = ora.conv2d(x, w["conv.weight"].astype(np.float16), w["conv.bias"], padding=(1, 1)).astype(np.float32)
+    s = w["bn.weight"] / np.sqrt(w["bn.var"] + np.float32(1e-5))
+    want = np.maximum(c * s[None, :, None, None] + (w["bn.bias"] - w["bn.mean"] * s)[None, :, None, None], 0)
+    assert np.max(np.abs(folded - want)) < 2e-2 * max(1.0, float(np.max(np.abs(want))))
+    assert foldbatchnorm(g, w) == 0 and foldrelu(g) == 0 and hoistcasts(g, w) == 0
