@@ -175,6 +175,7 @@ def kernel_figures(ctx, jv, pk, quick: bool):
     def att():
         q, k, v, o = sets[i[0] % 4]
         i[0] += 1
+        ctx.ws.reset()
         jv.sdpa(ctx, q, k, v, None, 0.125, out=o)
 
     for _ in range(3):
@@ -204,9 +205,14 @@ def kernel_figures(ctx, jv, pk, quick: bool):
     out["conv_stem_1024x1024x3_7x7s4_to_112"] = dict(ms=round(ms, 5), tflops=round(2.0 * 65536 * 147 * 112 / ms / 1e9, 2),
                                                      note="im2col (19 MB) + GEMM; HBM/latency-bound, not tensor-bound")
     Bw, Hw, Lw, Ew = 1024, 2, 64, 56
-    q, k, v = (ctx.toback(np.float16(rng.standard_normal((Bw, Hw, Lw, Ew), dtype=np.float32))) for _ in range(3))
-    ow = ctx.allocate(np.float16, Ew, Lw, Hw, Bw)
-    watt = lambda: jv.sdpa(ctx, q, k, v, None, 1.0 / np.sqrt(Ew), out=ow)
+    # operands as the image encoder hands them over: one token-major q/k/v projection (3d, tokens) with the
+    # tokens of a window adjacent, read through strides; the result token-major as well
+    dw = Hw * Ew
+    qkv = ctx.toback(np.float16(rng.standard_normal((Bw * Lw, 3 * dw), dtype=np.float32)))
+    part = lambda i: jv.DeviceArray(ctx, qkv.ptr + i * dw * 2, np.float16, (Ew, Lw, Hw, Bw), (1, 3 * dw, Ew, 3 * dw * Lw), owner=qkv)
+    obuf = ctx.allocate(np.float16, dw, Lw * Bw)
+    ow = jv.DeviceArray(ctx, obuf.ptr, np.float16, (Ew, Lw, Hw, Bw), (1, dw, Ew, dw * Lw), owner=obuf)
+    watt = lambda: (ctx.ws.reset(), jv.sdpa(ctx, part(0), part(1), part(2), None, 1.0 / np.sqrt(Ew), out=ow))
     for _ in range(3):
         watt()
     ctx.synchronize()

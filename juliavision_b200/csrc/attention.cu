@@ -63,9 +63,10 @@ struct AttnParams {
     // only see the keys of its own window, i / dq == key / dk.  0 = no packing.
     int dq, dk;
     // Keys split over nsplit CTAs per query pair (few queries, many keys): each writes its unnormalised
-    // fp32 O rows to part_o[split][b][h][lq][E] and (reference point, row sum) to part_ml[...][2];
+    // fp32 O rows to part_o[split][tail pair][256 rows][E] and (reference point, row sum) to part_ml[...][2];
     // attention_merge_kernel combines them (the reference's attn_flash_cm_merge!, flash.jl:1398-1421).
     int nsplit;
+    int ntail;          // pairs that are split (the last ntail of them)
     float* part_o;
     float* part_ml;
 };
@@ -134,23 +135,29 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
     // Work item of this CTA.  Most CTAs own a pair of query tiles; when the pairs do not fill the
     // last wave of SMs, the pairs of that wave are handed out as single tiles instead (twice as
     // many, half as long), which shortens the tail.
-    int item = blockIdx.x, half = -1;
+    // CTAs [0, pair_ctas) own a whole pair.  The pairs after those are the tail: either each is cut along
+    // the keys into nsplit CTAs whose partial results are merged afterwards (nsplit > 1), or each is
+    // handed out as two single tiles.
+    int item = blockIdx.x, half = -1, split = 0, nsp = 1;
     if (item >= p.pair_ctas) {
-        half = (item - p.pair_ctas) & 1;
-        item = p.pair_ctas + ((item - p.pair_ctas) >> 1);
+        const int t = item - p.pair_ctas;
+        if (p.nsplit > 1) {
+            nsp = p.nsplit;
+            split = t % nsp;
+            item = p.pair_ctas + t / nsp;
+        } else {
+            half = t & 1;
+            item = p.pair_ctas + (t >> 1);
+        }
     }
-    int split = 0;
-    if (p.nsplit > 1) {
-        split = item % p.nsplit;
-        item /= p.nsplit;
-    }
+    const int tailpair = item - p.pair_ctas;   // index among the split pairs (when nsp > 1)
     const int qp = item % p.qpairs;
     const int h = (item / p.qpairs) % p.H;
     const int b = item / (p.qpairs * p.H);
     const int q0 = qp * (2 * ATT_BR) + (half > 0 ? ATT_BR : 0);
     const int nblk_all = (p.Lk + ATT_BC - 1) / ATT_BC;
-    const int jb0 = p.nsplit > 1 ? (int)((int64_t)split * nblk_all / p.nsplit) : 0;           // first key block of this CTA
-    const int nblk = (p.nsplit > 1 ? (int)((int64_t)(split + 1) * nblk_all / p.nsplit) : nblk_all) - jb0;
+    const int jb0 = (int)((int64_t)split * nblk_all / nsp);           // first key block of this CTA
+    const int nblk = (int)((int64_t)(split + 1) * nblk_all / nsp) - jb0;
     const int ntiles = (half < 0 && q0 + ATT_BR < p.Lq) ? 2 : 1;   // the second tile may lie wholly past Lq
 
     if (threadIdx.x == 0) {
@@ -455,11 +462,11 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
             if (ok) {
                 tc_fence_after();
                 const int lq = q0 + t * ATT_BR + row;
-                if (p.nsplit > 1) {
+                if (nsp > 1) {
                     // Unnormalised rows and their (reference point, sum) for the merge.  tcgen05.ld is a
                     // warp-wide (.sync.aligned) instruction: every lane executes it, whether or not its
                     // row exists; only the stores are predicated.
-                    const int64_t prow = (((int64_t)split * p.B + b) * p.H + h) * p.Lq + (lq < p.Lq ? lq : 0);
+                    const int64_t prow = ((int64_t)split * p.ntail + tailpair) * (2 * ATT_BR) + t * ATT_BR + row;
                     float* po = p.part_o + prow * p.E;
 #pragma unroll 1
                     for (int c = 0; c < ATT_EP / 32; ++c) {
@@ -533,14 +540,18 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
 // Combine the partial results of a key split (attn_flash_cm_merge!, flash.jl:1398-1421): one warp per
 // query row; out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M the largest reference point.
 __global__ void __launch_bounds__(128)
-attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nsplit, int E, int Lq, int H,
-                       int B, void* out, int64_t osL, int64_t osH, int64_t osB, int out_f32) {
+attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nsplit, int ntail,
+                       int first_pair, int qpairs, int E, int Lq, int H, void* out, int64_t osL, int64_t osH, int64_t osB,
+                       int out_f32) {
     grid_dep_wait();
     const int lane = threadIdx.x & 31;
-    const int64_t rows = (int64_t)Lq * H * B;
+    const int64_t rows = (int64_t)ntail * (2 * ATT_BR);
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
-    const int lq = (int)(row % Lq), h = (int)((row / Lq) % H), b = (int)(row / ((int64_t)Lq * H));
+    const int pair = first_pair + (int)(row / (2 * ATT_BR));
+    const int lq = (pair % qpairs) * (2 * ATT_BR) + (int)(row % (2 * ATT_BR));
+    if (lq >= Lq) return;
+    const int h = (pair / qpairs) % H, b = pair / (qpairs * H);
     float M = -INFINITY;
     for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(s * rows + row) * 2]);
     float den = 0.f, num0 = 0.f, num1 = 0.f;
@@ -783,37 +794,49 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
     const int64_t pairs = (int64_t)p.qpairs * H * B;
     B200_REQUIRE(pairs < (1ll << 30), B200_DECLINE_EXTENT, "attention: too many query tiles");
     const int64_t sms = ctx->prop.multiProcessorCount;
-    // Few queries over many keys (a decode step: Lq = 23, Lk = 4096) would leave most SMs idle: split
-    // the keys over several CTAs per query pair, at least two key blocks each, and merge.
+    // Two cases cut pairs along the keys (at least two key blocks per piece) and merge afterwards:
+    // few queries over many keys (a decode step, Lq = 23, Lk = 4096: every pair is cut so that the
+    // SMs are all used), and a last wave that would leave most SMs idle (its pairs are cut so that
+    // the wave is as short as the cut allows instead of a whole pair long).
     p.nsplit = 1;
+    p.ntail = 0;
     p.part_o = p.part_ml = nullptr;
     const int64_t nblk_all = cdiv(Lk, ATT_BC);
-    if (bptr == nullptr && pack_dq == 0 && 2 * pairs <= sms && nblk_all >= 4) {
-        int64_t ns = sms / pairs;
+    const int64_t rem = pairs % sms;
+    if (bptr == nullptr && pack_dq == 0 && nblk_all >= 4) {
+        int64_t ntail = 0, ns = 1;
+        if (2 * pairs <= sms) {
+            ntail = pairs;
+            ns = sms / pairs;
+        } else if (pairs > sms && rem > 0 && 2 * rem <= sms) {
+            ntail = rem;
+            ns = sms / rem;
+        }
         if (ns > nblk_all / 2) ns = nblk_all / 2;
         if (ns > 64) ns = 64;
-        if (ns >= 2) {
-            const int64_t rows = Lq * H * B;
+        if (ntail > 0 && ns >= 2) {
+            const int64_t rows = ntail * 2 * ATT_BR;
             void* ws = nullptr;
             rc = ws_scratch(ctx, (size_t)(ns * rows * (E + 2)) * sizeof(float), &ws);
             if (rc) return rc;
             p.nsplit = (int)ns;
+            p.ntail = (int)ntail;
             p.part_o = static_cast<float*>(ws);
             p.part_ml = p.part_o + ns * rows * E;
         }
     }
     if (p.nsplit > 1) {
-        p.pair_ctas = (int)(pairs * p.nsplit);
-        B200_CUDA(launch_dep(attention_f16_tc_kernel<false>, dim3((unsigned)(pairs * p.nsplit), 1, 1), dim3(ATT_THREADS, 1, 1),
+        p.pair_ctas = (int)(pairs - p.ntail);
+        const int64_t ctas = p.pair_ctas + (int64_t)p.ntail * p.nsplit;
+        B200_CUDA(launch_dep(attention_f16_tc_kernel<false>, dim3((unsigned)ctas, 1, 1), dim3(ATT_THREADS, 1, 1),
                              ATT_SMEM_BYTES, ctx->stream, 1, tq, tk, tv, p));
-        const int64_t rows = Lq * H * B;
+        const int64_t rows = (int64_t)p.ntail * 2 * ATT_BR;
         B200_CUDA(launch_dep(attention_merge_kernel, dim3((unsigned)cdiv(rows, 4), 1, 1), dim3(128, 1, 1), 0, ctx->stream, 1,
-                             (const float*)p.part_o, (const float*)p.part_ml, p.nsplit, (int)E, (int)Lq, (int)H, (int)B, out,
-                             o->stride[1], o->stride[2], o->stride[3], (int)(out_dtype == B200_F32)));
+                             (const float*)p.part_o, (const float*)p.part_ml, p.nsplit, p.ntail, p.pair_ctas, p.qpairs, (int)E,
+                             (int)Lq, (int)H, out, o->stride[1], o->stride[2], o->stride[3], (int)(out_dtype == B200_F32)));
         ctx->launches += 2;
         return B200_OK;
     }
-    const int64_t rem = pairs % sms;
     // Split the pairs of a last wave that would leave more than half of the SMs idle — but not a
     // pair whose second tile does not exist.
     int64_t nsplit = (pairs > sms && rem > 0 && 2 * rem <= sms && Lq % (2 * ATT_BR) == 0) ? rem : 0;

@@ -64,6 +64,7 @@ def attention(ctx, a):
     def go():
         q, k, v, o = sets[i[0] % a.buffers]
         i[0] += 1
+        ctx.ws.reset()     # one op per call: a key split's partial results reuse the same scratch
         jv.sdpa(ctx, q, k, v, None, 1.0 / np.sqrt(a.head_dim), out=o)
 
     ms = _time(ctx, go, a.reps)
