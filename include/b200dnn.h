@@ -36,7 +36,7 @@ enum {
     B200_DECLINE_OPERANDS = 16,  /* :operands  dtype/rank the fast path does not take */
     B200_DECLINE_EXTENT = 17,    /* :extent    an extent the tiling cannot cover      */
     B200_DECLINE_ALIGN = 18,     /* :wrapped   stride/pointer a TMA map cannot express*/
-    B200_DECLINE_BIAS = 19,      /* :bias      additive attention mask present        */
+    B200_DECLINE_BIAS = 19,      /* :bias      a bias/mask of a shape the op cannot take */
     B200_DECLINE_ELTYPE = 20,    /* :eltype                                            */
     B200_DECLINE_TILING = 21     /* :tiling    no tile shape fits                      */
 };
