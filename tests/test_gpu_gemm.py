@@ -210,3 +210,32 @@ def test_gemv_one_token(ctx, ora, dtype, M, K):
             from scipy.special import erf
             ref = {"identity": want, "relu": np.maximum(want, 0), "gelu": 0.5 * want * (1 + erf(want / np.sqrt(2)))}[epi]
             assert relerr(got, ref) < 1e-4, describe(got, ref, 1e-4)
+
+
+def test_timeline_records_time_and_cycles(ctx):
+    """b200_timeline: worker 0's events in nanoseconds and in SM cycles; their ratio is a plausible clock,
+    the events are in order, every worker's exit is recorded, and nothing is written once it is off."""
+    import ctypes as C
+    from juliavision_b200 import _lib
+    rng = np.random.default_rng(1)
+    X = ctx.toback(np.float16(rng.standard_normal((2048, 1024), dtype=np.float32) * 0.05))
+    W = ctx.toback(np.float16(rng.standard_normal((1024, 2048), dtype=np.float32) * 0.05))
+    out = ctx.allocate(np.float16, 2048, 2048)
+    tl = ctx.allocate(np.uint64, 256)
+    ctx.fill_bytes(tl, 0)
+    jv.matmul_(ctx, out, W, X, None)
+    ctx.synchronize()
+    _lib.check(_lib.lib().b200_timeline(ctx.handle, tl.ptr))
+    jv.matmul_(ctx, out, W, X, None)
+    ctx.synchronize()
+    _lib.check(_lib.lib().b200_timeline(ctx.handle, None))
+    t = tl.to_host().astype(np.int64)
+    assert 0 < t[0] <= t[1] <= t[3] <= t[4] <= t[8] <= t[12] <= t[16]          # entry .. exit, in order
+    ns, clk = t[16] - t[0], t[64 + 16] - t[64 + 0]
+    assert ns > 0 and 500 < clk / ns * 1e3 < 2200                               # MHz
+    exits = t[128:128 + 120]
+    assert 1 <= np.count_nonzero(exits) <= 120 and np.all(exits[exits > 0] >= t[0])   # one per worker
+    ctx.fill_bytes(tl, 0)
+    jv.matmul_(ctx, out, W, X, None)
+    ctx.synchronize()
+    assert not tl.to_host().any()
