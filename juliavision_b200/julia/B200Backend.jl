@@ -14,9 +14,9 @@
 
 module B200
 
-using ..DNNKernels: Ctx, Decline, accum, actfn, geluexact, gelutanh, relu_epi
-import ..DNNKernels: matmul!, mmplan, batchedmatmul!, sdpa!, sdpaplan, layernorm!, convolution!,
-                     scratch!, toback, caps, slabview
+using ..DNNKernels: Ctx, Decline, MMGemvPlan, accum, actfn, geluexact, gelutanh, relu_epi
+import ..DNNKernels: matmul!, mmplan, mm_gemv_plan, batchedmatmul!, sdpa!, sdpaplan, layernorm!, convolution!,
+                     maxpool2d!, scratch!, toback, caps, slabview
 import KernelAbstractions
 
 const LIB = get(ENV, "B200DNN_LIB", "libb200dnn.so")
@@ -136,6 +136,10 @@ end
 
 # ------------------------------------------------------------------ matmul! (matmul.jl:78-100)
 function mmplan(dev::B200Caps, out, A, B, bias)
+    if size(B, 2) == 1                       # one token: the matrix-vector kernel (fp32 as in the reference, or fp16)
+        g = mm_gemv_plan(dev, out, A, B, bias)
+        g isa MMGemvPlan && return g
+    end
     eltype(A) === Float16 && eltype(B) === Float16 || return Decline(:operands)
     eltype(out) in (Float16, Float32) || return Decline(:eltype)
     ra, rb, ro = rootstrides(A), rootstrides(B), rootstrides(out)
