@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(CSRC, "libb200dnn.so")
 SOURCES = ["ctx.cu", "layernorm.cu", "gemm.cu", "attention.cu", "glue.cu", "conv.cu", "gemv.cu"]
-HEADERS = ["internal.h", "ptx.cuh", os.path.join("..", "..", "include", "b200dnn.h")]
+HEADERS = ["internal.h", "ptx.cuh", "act.cuh", os.path.join("..", "..", "include", "b200dnn.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

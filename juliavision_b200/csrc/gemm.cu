@@ -21,6 +21,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include "act.cuh"
 #include "internal.h"
 #include "ptx.cuh"
 
@@ -82,39 +83,6 @@ template <typename OutT> struct GemmParams {
             p.trace[64 + (slot)] = (unsigned long long)clock64();          \
         }                                                                  \
     } while (0)
-
-__device__ __forceinline__ float erf_as(float x) {
-    // Abramowitz & Stegun 7.1.26 in fp32, the reference's erf (ops.jl:161-169).
-    float a = fabsf(x);
-    float t = __fdividef(1.0f, 1.0f + 0.3275911f * a);
-    float y = 1.0f - (((((1.061405429f * t - 1.453152027f) * t) + 1.421413741f) * t - 0.284496736f) * t +
-                      0.254829592f) * t * __expf(-a * a);
-    return x < 0.f ? -y : y;
-}
-// geluexact on the fp16-rounded value: 0.5 x (1 + erf(x/sqrt2)), A&S erf, fp32 (ops.jl:1665-1670).
-__device__ __forceinline__ float gelu_exact(float x) {
-    const float z = x * 0.70710678118654752f;
-    const float a = fabsf(z);
-    float t;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, a, 1.0f)));
-    float e;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-a * a * 1.4426950408889634f));
-    const float poly = ((((1.061405429f * t - 1.453152027f) * t + 1.421413741f) * t - 0.284496736f) * t + 0.254829592f) * t;
-    const float y = fmaf(-poly, e, 1.0f);          // erf(|z|)
-    const float hx = 0.5f * x;
-    return fmaf(hx, copysignf(y, z), hx);
-}
-__device__ __forceinline__ float apply_act(int epi, float v) {
-    switch (epi) {
-        case B200_EPI_RELU: return fmaxf(v, 0.f);
-        case B200_EPI_GELU: return gelu_exact(v);
-        case B200_EPI_GELU_TANH: {
-            float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-            return 0.5f * v * (1.0f + tanhf(u));
-        }
-        default: return v;
-    }
-}
 
 // The work of one worker (a CTA, or a CTA pair) as a sequence of segments, a segment being the
 // k-blocks [kb0, kb1) of one tile.

@@ -6,28 +6,11 @@
 // workspace, summed in a fixed order by a second small kernel, so the result does not depend on timing).
 #include <cuda_fp16.h>
 
+#include "act.cuh"
 #include "internal.h"
 
 namespace b200 {
 
-__device__ __forceinline__ float gemv_erf(float x) {
-    float a = fabsf(x);
-    float t = __fdividef(1.0f, 1.0f + 0.3275911f * a);
-    float y = 1.0f - (((((1.061405429f * t - 1.453152027f) * t) + 1.421413741f) * t - 0.284496736f) * t +
-                      0.254829592f) * t * __expf(-a * a);
-    return x < 0.f ? -y : y;
-}
-__device__ __forceinline__ float gemv_act(int epi, float v) {
-    switch (epi) {
-        case B200_EPI_RELU: return fmaxf(v, 0.f);
-        case B200_EPI_GELU: return 0.5f * v * (1.0f + gemv_erf(v * 0.70710678118654752f));
-        case B200_EPI_GELU_TANH: {
-            float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-            return 0.5f * v * (1.0f + tanhf(u));
-        }
-        default: return v;
-    }
-}
 template <typename T> __device__ __forceinline__ float gemv_tof(T v);
 template <> __device__ __forceinline__ float gemv_tof<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float gemv_tof<float>(float v) { return v; }
@@ -35,8 +18,8 @@ template <> __device__ __forceinline__ float gemv_tof<float>(float v) { return v
 // The activation sees the value rounded to the output type (ops.jl:161-169), as in the GEMM's store.
 template <typename OutT>
 __device__ __forceinline__ void gemv_store(OutT* out, int64_t m, float acc, int epi) {
-    if constexpr (sizeof(OutT) == 2) out[m] = __float2half_rn(gemv_act(epi, __half2float(__float2half_rn(acc))));
-    else out[m] = gemv_act(epi, acc);
+    if constexpr (sizeof(OutT) == 2) out[m] = __float2half_rn(apply_act(epi, __half2float(__float2half_rn(acc))));
+    else out[m] = apply_act(epi, acc);
 }
 
 constexpr int GEMV_WARPS = 8;

@@ -4,28 +4,10 @@
 // 323-335, 1698-1702; execute.jl:257-277).
 #include <cuda_fp16.h>
 
+#include "act.cuh"
 #include "internal.h"
 
 namespace b200 {
-
-__device__ __forceinline__ float glue_erf(float x) {
-    float a = fabsf(x);
-    float t = __fdividef(1.0f, 1.0f + 0.3275911f * a);
-    float y = 1.0f - (((((1.061405429f * t - 1.453152027f) * t) + 1.421413741f) * t - 0.284496736f) * t +
-                      0.254829592f) * t * __expf(-a * a);
-    return x < 0.f ? -y : y;
-}
-__device__ __forceinline__ float glue_act(int epi, float v) {
-    switch (epi) {
-        case B200_EPI_RELU: return fmaxf(v, 0.f);
-        case B200_EPI_GELU: return 0.5f * v * (1.0f + glue_erf(v * 0.70710678118654752f));
-        case B200_EPI_GELU_TANH: {
-            float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-            return 0.5f * v * (1.0f + tanhf(u));
-        }
-        default: return v;
-    }
-}
 
 enum { OP_ADD = 0, OP_CLAMP = 1, OP_ACT = 2 };
 
@@ -33,7 +15,7 @@ template <int OP>
 __device__ __forceinline__ float ew(float a, float b, float lo, float hi, int epi) {
     if (OP == OP_ADD) return a + b;
     if (OP == OP_CLAMP) return fminf(fmaxf(a, lo), hi);
-    return glue_act(epi, a);
+    return apply_act(epi, a);
 }
 
 // 8 halfs (16 B) per thread per step, grid-stride; the scalar tail is handled by the last
