@@ -322,6 +322,95 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_hiera(args):
+    """The image workload of the scaling sweep: `--images` 1024x1024 images per GPU (64 images over 8 GPUs =
+    8 each) through the Hiera-B+-shaped encoder, one pass per step replayed as a CUDA graph; images are
+    independent, so ranks share nothing but the closing barrier."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    import ctypes as C
+    import torch
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import juliavision_b200 as jv
+    from juliavision_b200 import _lib
+    from juliavision_b200.hiera import Hiera, HieraConfig
+    cfg, nb = HieraConfig(), args.images
+    warmup = max(args.warmup, 3)
+    ctx = jv.Ctx(local)
+    model = Hiera(ctx, cfg, batch=nb)
+    img = np.float16(np.random.default_rng(21 + rank).random((nb, cfg.in_ch, cfg.image, cfg.image), dtype=np.float32))
+    hx, hy = C.c_void_p(), C.c_void_p()
+    _lib.check(_lib.lib().b200_host_alloc(img.nbytes, C.byref(hx)))
+    _lib.check(_lib.lib().b200_host_alloc(model.y.nbytes, C.byref(hy)))
+    C.memmove(hx.value, img.ctypes.data, img.nbytes)
+    ctx.upload(model.image, img)
+    per_pass = model.launches_per_pass()
+    graph = model.capture()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        ctx.synchronize()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    for _ in range(warmup):
+        graph.replay()
+    barrier()
+    ctx.timer_start()
+    for _ in range(args.steps):
+        graph.replay()
+    ms_step = ctx.timer_stop() / args.steps
+    barrier()
+
+    def e2e_step():
+        _lib.check(_lib.lib().b200_upload_async(ctx.handle, model.image.ptr, hx, img.nbytes))
+        graph.replay()
+        _lib.check(_lib.lib().b200_download_async(ctx.handle, hy, model.y.ptr, model.y.nbytes))
+        ctx.synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    ctx.timer_start()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e_ms = ctx.timer_stop() / args.steps
+    barrier()
+    clocks = sampler.stop()
+    if dist is not None:
+        t = torch.tensor([ms_step, e2e_ms], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, e2e_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        imgs = nb * world
+        print(json.dumps(dict(
+            metric="hiera_ms_per_img", value=round(ms_step / imgs, 4), unit="ms/img", n_gpus=world, steps=args.steps,
+            warmup=warmup, ms_per_step=round(ms_step, 4), higher_is_better=False, scaling="weak", vs_baseline=None,
+            dtype="f16 (fp32 accumulate)", data="synthetic",
+            config=dict(workload=f"configs 4/5: Hiera-B+-shaped encoder, {cfg.image}x{cfg.image}x{cfg.in_ch} images, "
+                                 f"{nb} per GPU per step, depths {cfg.depths}, embed {cfg.embed}, windows {cfg.windows}, "
+                                 f"global blocks {cfg.global_blocks}",
+                        parallelism=f"batch-sharded x{world}, weights replicated, no collective",
+                        l2="inputs larger than L2: each pass streams its images and 0.14 GB of weights", replay="cuda graph",
+                        imgs_per_step=imgs, tflops_per_gpu=round(cfg.flops(nb) / ms_step / 1e9, 1)),
+            e2e=dict(value=round(e2e_ms / imgs, 4), unit="ms/img", h2d_bytes_per_step=int(img.nbytes),
+                     d2h_bytes_per_step=int(model.y.nbytes)),
+            gpu_launches=per_pass * args.steps, roofline=None, clocks=clocks, cpu_baseline=None)), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    _lib.lib().b200_host_free(hx)
+    _lib.lib().b200_host_free(hy)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -331,10 +420,15 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="encoder depth (32 = the named config)")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel figures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--workload", default="encoder", choices=["encoder", "hiera"],
+                    help="encoder = the headline config-3 stack; hiera = the image workload of the scaling sweep")
+    ap.add_argument("--images", type=int, default=8, help="images per GPU per step for --workload hiera")
     ap.add_argument("--cpu-layers", type=int, default=10, help="layers of the CPU baseline sample (about 1 s each on 16 cores)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "hiera":
+        return run_hiera(args)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
