@@ -29,7 +29,7 @@ constexpr int ATT_THREADS = 384;  // warps 0-3, 4-7: softmax of tile 0, 1; warp 
 constexpr int ATT_TILE_BYTES = 128 * 128; // every operand tile is 128 rows x 128 B
 constexpr int ATT_KV_STAGES = 4;
 #ifndef ATT_TURN_AT
-#define ATT_TURN_AT 1   // after which quarter (0..3) of its exponentials a tile passes the turn
+#define ATT_TURN_AT 2   // after which quarter (0..3) of its exponentials a tile passes the turn
 #endif
 // shared-memory map, in 16 KB tiles
 constexpr int ATT_T_Q = 0;                         // 2 tiles
