@@ -166,6 +166,21 @@ template <typename T>
 static int launch_permute(b200_ctx* ctx, const void* src, void* out, const int64_t* d, const int64_t* s) {
     const int64_t n = d[0] * d[1] * d[2] * d[3];
     if (n == 0) return B200_OK;
+    // Axis 0 contiguous on both sides (a window partition moves whole runs of channels): the same gather
+    // in 16-byte pieces.
+    constexpr int64_t V = 16 / (int64_t)sizeof(T);
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (s[0] == 1 && d[0] % V == 0 && s[1] % V == 0 && s[2] % V == 0 && s[3] % V == 0 && al16(src) && al16(out)) {
+        const int64_t nv = n / V;
+        int64_t blocks = cdiv(nv, 256);
+        const int64_t cap = (int64_t)ctx->prop.multiProcessorCount * 32;
+        if (blocks > cap) blocks = cap;
+        permute4_kernel<uint4><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const uint4*)src, (uint4*)out, nv, d[0] / V, d[1], d[2],
+                                                                         1, s[1] / V, s[2] / V, s[3] / V);
+        ctx->launches++;
+        B200_CUDA(cudaGetLastError());
+        return B200_OK;
+    }
     if (s[1] == 1 && s[0] != 1 && d[0] < (1ll << 30) && d[1] < (1ll << 30) && d[2] * d[3] < 65536 &&
         cdiv(d[1], 32) < 65536) {
         dim3 grid((unsigned)cdiv(d[0], 32), (unsigned)cdiv(d[1], 32), (unsigned)(d[2] * d[3]));

@@ -110,6 +110,12 @@ def test_permute_bit_exact(ctx):
     f = np.float32(rng.standard_normal((3, 4, 50, 33)))
     df = ctx.toback(f)
     assert np.array_equal(ctx.contiguous(df.permute((1, 0, 3, 2))).to_host(), f.transpose(1, 0, 3, 2))
+    # axis 0 kept in front: 16-byte pieces when its extent and the strides allow, element by element when not
+    for shape, dt in (((4, 9, 6, 64), np.float16), ((2, 5, 7, 20), np.float16), ((3, 6, 5, 8), np.float32), ((2, 3, 4, 6), np.float32)):
+        g = rng.standard_normal(shape).astype(dt)
+        dg = ctx.toback(g)
+        assert np.array_equal(ctx.contiguous(dg.permute((0, 2, 1, 3))).to_host(), g.transpose(0, 2, 1, 3))
+        assert np.array_equal(ctx.contiguous(dg.permute((0, 3, 2, 1))).to_host(), g.transpose(2, 1, 0, 3))
 
 
 def test_pool_and_workspace(ctx):
