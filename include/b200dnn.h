@@ -220,7 +220,8 @@ int b200_add_layernorm_f16(b200_ctx* ctx, int64_t groups, int64_t C, void* x, co
 /* ------------------------------------------------------- convolution as a GEMM */
 /*
  * im2col_kernel! (conv_coopmat.jl:246-289): col (MP,CRSP) fp16 column-major from
- * x (W,H,Cin,N); rows >= NPQ, columns >= KW*KH*Cin and out-of-image taps are zero.
+ * x (W,H,Cin,N); rows >= NPQ, columns >= KW*KH*Cin and out-of-image taps are zero.  MP (the
+ * padded row count) must be a multiple of 8 and col 16-byte aligned: rows leave in 16-byte stores.
  */
 int b200_im2col_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW,
                     int64_t KH, int64_t sx, int64_t sy, int64_t px, int64_t py, int64_t dx,

@@ -10,32 +10,45 @@
 
 namespace b200 {
 
-// col (MP, CRSP) column-major: thread -> (m, c) with m fastest so the writes coalesce.
+// col (MP, CRSP) column-major: a thread produces eight consecutive rows m of one column c (one
+// 16-byte store), so the column's (kw, kh, cin) is decomposed once per eight elements and the pixel
+// index advances incrementally; neighbouring threads take neighbouring m, so the stores coalesce.
 // Index math is 32-bit on purpose: every extent is far inside int32 and 64-bit division
-// is emulated (same observation as the reference, conv_coopmat.jl:238-245).
+// is emulated (same observation as the reference, conv_coopmat.jl:238-245).  MP is a multiple of 8.
 __global__ void __launch_bounds__(256)
 im2col_f16_kernel(__half* __restrict__ col, const __half* __restrict__ x, int MP, int CRSP, int KW, int KH,
                   int sx, int sy, int px, int py, int dx, int dy, int Wid, int Hei, int OW, int OH, int NPQ,
-                  int Cin, int64_t ntot) {
-    for (int64_t lin = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; lin < ntot;
+                  int Cin, int64_t ntot8) {
+    const int MP8 = MP >> 3;
+    for (int64_t lin = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; lin < ntot8;
          lin += (int64_t)gridDim.x * blockDim.x) {
-        const int m = (int)(lin % MP);
-        const int c = (int)(lin / MP);
-        __half v = __float2half(0.f);
-        if (m < NPQ) {
-            const int n = m / (OH * OW);
-            const int r = m - n * (OH * OW);
-            const int oh = r / OW, ow = r - oh * OW;
-            const int kw = c % KW, t = c / KW;
-            const int kh = t % KH, cin = t / KH;
-            if (cin < Cin) {
+        const int m0 = (int)(lin % MP8) * 8;
+        const int c = (int)(lin / MP8);
+        const int kw = c % KW, t = c / KW;
+        const int kh = t % KH, cin = t / KH;
+        __align__(16) __half v[8];
+        int n = m0 / (OH * OW);
+        int r = m0 - n * (OH * OW);
+        int oh = r / OW, ow = r - oh * OW;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            __half val = __float2half(0.f);
+            if (m0 + e < NPQ && cin < Cin) {
                 const int ix = ow * sx - px + kw * dx;
                 const int iy = oh * sy - py + kh * dy;
                 if (ix >= 0 && ix < Wid && iy >= 0 && iy < Hei)
-                    v = x[ix + (int64_t)Wid * (iy + (int64_t)Hei * (cin + (int64_t)Cin * n))];
+                    val = x[ix + (int64_t)Wid * (iy + (int64_t)Hei * (cin + (int64_t)Cin * n))];
+            }
+            v[e] = val;
+            if (++ow == OW) {
+                ow = 0;
+                if (++oh == OH) {
+                    oh = 0;
+                    ++n;
+                }
             }
         }
-        col[lin] = v;
+        *reinterpret_cast<uint4*>(col + (int64_t)c * MP + m0) = *reinterpret_cast<const uint4*>(v);
     }
 }
 
@@ -78,13 +91,15 @@ int b200_im2col_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N,
     B200_REQUIRE(OW > 0 && OH > 0, B200_DECLINE_EXTENT, "im2col: empty output");
     const int64_t NPQ = OW * OH * N;
     B200_REQUIRE(MP >= NPQ && CRSP >= KW * KH * Cin, B200_EINVAL, "im2col: MP/CRSP below the real extents");
+    B200_REQUIRE(MP % 8 == 0 && (reinterpret_cast<uintptr_t>(col) & 15u) == 0, B200_DECLINE_ALIGN,
+                 "im2col: MP must be a multiple of 8 and col 16-byte aligned");
     B200_REQUIRE(MP < (1ll << 31) && CRSP < (1ll << 31) && W * H * Cin < (1ll << 31), B200_DECLINE_EXTENT,
                  "im2col: extent beyond int32");
     B200_CUDA(cudaSetDevice(ctx->device));
-    const int64_t ntot = MP * CRSP;
-    im2col_f16_kernel<<<grid_for(ctx, ntot), 256, 0, ctx->stream>>>(
+    const int64_t ntot8 = MP / 8 * CRSP;
+    im2col_f16_kernel<<<grid_for(ctx, ntot8), 256, 0, ctx->stream>>>(
         (__half*)col, (const __half*)x, (int)MP, (int)CRSP, (int)KW, (int)KH, (int)sx, (int)sy, (int)px, (int)py,
-        (int)dx, (int)dy, (int)W, (int)H, (int)OW, (int)OH, (int)NPQ, (int)Cin, ntot);
+        (int)dx, (int)dy, (int)W, (int)H, (int)OW, (int)OH, (int)NPQ, (int)Cin, ntot8);
     ctx->launches++;
     B200_CUDA(cudaGetLastError());
     return B200_OK;
