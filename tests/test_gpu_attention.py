@@ -203,7 +203,9 @@ def test_many_small_windows_packed(ctx, ora, B, H, Lq, Lk, E):
     assert np.array_equal(got2[0::2], got[0::2])
 
 
-@pytest.mark.parametrize("B,H,Lq,Lk,E", [(1, 8, 23, 4096, 64), (2, 3, 1, 4000, 56), (1, 1, 300, 2048, 32), (1, 20, 130, 1500, 64)])
+@pytest.mark.parametrize("B,H,Lq,Lk,E", [(1, 8, 23, 4096, 64), (2, 3, 1, 4000, 56), (1, 1, 300, 2048, 32), (1, 20, 130, 1500, 64),
+                                         (1, 20, 2000, 2000, 64),     # 160 query pairs: the 12 of the last wave are cut, one of them ragged
+                                         (1, 39, 1000, 700, 40)])      # 156 pairs, 8 cut three ways, ragged queries and keys
 def test_few_queries_many_keys_split_and_merged(ctx, ora, B, H, Lq, Lk, E):
     """Decode-like shapes (flash.jl:298-323: Lq = 23, Lk = 4096): the keys are split over several CTAs
     per query tile and merged (attn_flash_cm_merge!); the values are those of the unsplit computation."""
