@@ -12,11 +12,11 @@
 // Replaces matmul_coopmat! + Lava.coopmat_gemm! + padcols_kernel! + mm_epilogue_kernel!
 // (reference kernels/extern/matmul.jl:172-273).
 //
-// Roles inside one persistent CTA (320 threads):
-//   warp 0    TMA producer  (one lane)        global -> shared ring, STAGES deep
-//   warp 1    UMMA issuer   (one lane)        shared -> TMEM accumulators (two, ping-pong)
-//   warps 2-9 epilogue      (256 threads)     TMEM -> registers -> +bias, round, act ->
-//                                             warp-private shared slab -> coalesced 16-byte stores
+// Roles inside one persistent CTA (576 threads):
+//   warp 0     TMA producer  (one lane)        global -> shared ring, STAGES deep
+//   warp 1     UMMA issuer   (one lane)        shared -> TMEM accumulators (two, ping-pong)
+//   warps 2-17 epilogue      (512 threads)     TMEM -> registers -> +bias, round, act ->
+//                                              warp-private shared slab -> bulk tensor store
 #include <cuda_fp16.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -143,6 +143,7 @@ template <int BN, typename OutT, int NCTA>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, tokens, batch}
                    const __grid_constant__ CUtensorMap tmapW,   // A(M,K): {features, K, batch}
+                   const __grid_constant__ CUtensorMap tmapO,   // out(M,N): {features, tokens, batch}, boxes of 16 x 32
                    const GemmParams<OutT> p) {
     using Cfg = GemmCfg<BN, OutT, NCTA>;
     constexpr int TILE_N = GEMM_BM * NCTA; // tokens per tile
@@ -184,6 +185,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         fence_barrier_init();
         prefetch_tmap(&tmapX);
         prefetch_tmap(&tmapW);
+        prefetch_tmap(&tmapO);
     }
     if (warp == 1) {
         if constexpr (NCTA == 2) {
@@ -304,16 +306,14 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
     } else {
         // ---------------------------------------------------------------- epilogue
         // Sixteen warps, four per TMEM lane quadrant, each taking every fourth chunk of 16 columns.
-        // Per chunk: tcgen05.ld -> +bias, round, activation -> a warp-private swizzled shared slab
-        // (32 rows x 16 columns) -> read back transposed (several lanes per output row) -> 16-byte
-        // global stores.  Each step is a short dependent chain, so the throughput comes from the
-        // four warps per scheduler taking turns; warps never wait for one another.
+        // Per chunk: tcgen05.ld -> +bias, round, activation -> a warp-private shared slab (32 rows x 16
+        // columns, plain rows) -> one bulk tensor store of the 16 x 32 box, clipped at the ragged edges
+        // of the output.  Each step is a short dependent chain, so the throughput comes from the four
+        // warps per scheduler taking turns; warps never wait for one another.
         constexpr int CH = 16;                 // columns per chunk (one tcgen05.ld.32x32b.x16)
         constexpr int NPART = EPI_WARPS / 4;   // warps sharing a lane quadrant
         constexpr int NCH = BN / NPART / CH;   // chunks one warp owns of a tile
         constexpr int RB = CH * (int)sizeof(OutT);  // staged bytes per row and chunk
-        constexpr int PPR = RB / 16;           // 16-byte pieces per staged row
-        constexpr int EPP = 16 / (int)sizeof(OutT); // elements per piece
         const int ew = warp - 2;               // 0..15
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
         const int part = ew >> 2;              // which chunks of the quadrant's rows
@@ -381,11 +381,9 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             tc_fence_after();
             if (ew == 0 && lane == 0) GEMM_TRACE(8 + (it < 4 ? it : 3)); // accumulator of tile `it` ready
 
-            OutT* gtile = p.out + (size_t)batch * p.strideO + (size_t)(n0 + quad * 32) * p.ldo + m0;
             const int rows_valid = (int)(p.N - (n0 + quad * 32));   // rows of this warp's slab inside the output
             const uint32_t tacc = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
             const int act_kind = p.epilogue;
-            const int sw = (lane / (8 / PPR)) % PPR;   // piece j of staged row r sits at piece j ^ swizzle(r)
             uint8_t* rowp = wstg + lane * RB;
 
 #pragma unroll 1
@@ -437,6 +435,10 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                 }
                 if (m0 + col0 >= p.M || rows_valid <= 0) continue; // nothing to write to the output
 
+                // the engine must have read the previous chunk out of the slab before it is overwritten; that
+                // read ran under this chunk's tcgen05.ld and arithmetic
+                if (lane == 0) tma_store_wait_read<0>();
+                __syncwarp();
                 // registers -> shared, lane = row
                 const float* bc = wbias + c * CH;
                 if constexpr (sizeof(OutT) == 2) {
@@ -452,7 +454,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                             h[1] = act(__floats2half2_rn(v[j * 8 + 2] + b0.z, v[j * 8 + 3] + b0.w));
                             h[2] = act(__floats2half2_rn(v[j * 8 + 4] + b1.x, v[j * 8 + 5] + b1.y));
                             h[3] = act(__floats2half2_rn(v[j * 8 + 6] + b1.z, v[j * 8 + 7] + b1.w));
-                            *reinterpret_cast<uint4*>(rowp + ((j ^ sw) << 4)) = o;
+                            *reinterpret_cast<uint4*>(rowp + (j << 4)) = o;
                         }
                     };
                     switch (act_kind) {
@@ -480,31 +482,17 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         o.y = apply_act(act_kind, v[j * 4 + 1] + b.y);
                         o.z = apply_act(act_kind, v[j * 4 + 2] + b.z);
                         o.w = apply_act(act_kind, v[j * 4 + 3] + b.w);
-                        *reinterpret_cast<float4*>(rowp + ((j ^ sw) << 4)) = o;
+                        *reinterpret_cast<float4*>(rowp + (j << 4)) = o;
                     }
                 }
-                __syncwarp();   // the staged chunk is visible to the lanes that will store it
-
-                // shared -> global: PPR lanes per row, 32/PPR rows per instruction.
-                const int pj = lane % PPR;
-                const int colp = col0 + pj * EPP;             // first feature column of this lane's piece
-                const int cvalid = (int)(p.M - m0) - colp;    // columns of the piece inside the output
-#pragma unroll
-                for (int rr = 0; rr < PPR; ++rr) {
-                    const int r = lane / PPR + (32 / PPR) * rr;
-                    const uint4 piece = *reinterpret_cast<const uint4*>(wstg + r * RB + ((pj ^ ((r / (8 / PPR)) % PPR)) << 4));
-                    if (r < rows_valid && cvalid > 0) {
-                        OutT* g = gtile + (size_t)r * p.ldo + colp;
-                        if (cvalid >= EPP) {
-                            *reinterpret_cast<uint4*>(g) = piece;
-                        } else {
-                            const OutT* e = reinterpret_cast<const OutT*>(&piece);
-                            for (int t = 0; t < EPP; ++t)
-                                if (t < cvalid) g[t] = e[t];
-                        }
-                    }
+                // shared -> global by the bulk-store engine: one instruction for the 16 x 32 box (plain rows in the
+                // slab), clipped at the ragged edges of the output.
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_3d(&tmapO, wstg, m0 + col0, n0 + quad * 32, batch);
+                    tma_store_commit();
                 }
-                __syncwarp(); // the slab is free for the next chunk
             }
             if (contributor) {
                 __threadfence();
@@ -518,6 +506,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             }
             if (ew == 0 && lane == 0) GEMM_TRACE(12 + (it < 4 ? it : 3)); // epilogue of tile `it` done
         }
+        if (lane == 0) tma_store_wait_all<0>();   // this warp's bulk stores have landed before the CTA leaves
     }
 
     // Teardown: every role arrives here whether it finished or gave up.
@@ -652,6 +641,16 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
                            CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
     }
+    CUtensorMap tO;
+    {
+        const uint64_t osz = sizeof(OutT);
+        uint64_t dims[3] = {(uint64_t)M, (uint64_t)N, (uint64_t)nbatch};
+        uint64_t str[2] = {(uint64_t)ldo * osz, (uint64_t)(nbatch > 1 ? sO : ldo * N) * osz};
+        uint32_t box[3] = {16, 32, 1};
+        int rc = make_tmap(ctx, &tO, sizeof(OutT) == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, out,
+                           dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+    }
     GemmParams<OutT> p;
     p.M = M; p.N = N; p.K = K;
     p.out = static_cast<OutT*>(out);
@@ -710,7 +709,7 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
         p.sk_part = static_cast<float*>(part);
     }
     B200_CUDA(launch_dep(kern, dim3((unsigned)(workers * NCTA), 1, 1), dim3(GEMM_THREADS, 1, 1), Cfg::SMEM_BYTES,
-                         ctx->stream, NCTA, tX, tW, p));
+                         ctx->stream, NCTA, tX, tW, tO, p));
     ctx->launches++;
     return B200_OK;
 }
