@@ -165,9 +165,9 @@ int b200_ctx_create(int device, b200_ctx** out) {
     e = cudaMalloc(&c->d_status, 256);
     if (e != cudaSuccess) { cudaStreamDestroy(c->stream); delete c; return fail_cuda(e, "cudaMalloc(status)"); }
     cudaMemset(c->d_status, 0, 256);
-    e = cudaMalloc(&c->sk_flags, SK_FLAG_COUNT * sizeof(int));
+    e = cudaMalloc(&c->sk_flags, (SK_FLAG_COUNT + GEMV_COUNTER_COUNT) * sizeof(int));
     if (e != cudaSuccess) { cudaFree(c->d_status); cudaStreamDestroy(c->stream); delete c; return fail_cuda(e, "cudaMalloc(flags)"); }
-    cudaMemset(c->sk_flags, 0, SK_FLAG_COUNT * sizeof(int));
+    cudaMemset(c->sk_flags, 0, (SK_FLAG_COUNT + GEMV_COUNTER_COUNT) * sizeof(int));
     cudaEventCreate(&c->ev0);
     cudaEventCreate(&c->ev1);
     void* fn = nullptr;

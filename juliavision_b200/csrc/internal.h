@@ -45,7 +45,8 @@ struct b200_ctx {
     cudaStream_t stream = nullptr;
     cudaDeviceProp prop{};
     int* d_status = nullptr;   // device status words: [0] first failed wait code
-    int* sk_flags = nullptr;   // stream-K hand-off flags (zero between launches), SK_FLAG_COUNT ints
+    int* sk_flags = nullptr;   // stream-K hand-off flags (zero between launches), SK_FLAG_COUNT ints, then
+                               // GEMV_COUNTER_COUNT arrival counters (zero between launches)
     int64_t launches = 0;
     bool capturing = false;
     unsigned long long* gemm_trace = nullptr;  // device buffer of >= 32 slots while tracing, else null
@@ -65,6 +66,7 @@ struct b200_ctx {
 };
 
 constexpr int SK_FLAG_COUNT = 4096;
+constexpr int GEMV_COUNTER_COUNT = 4096;   // arrival counters of the split matrix-vector product, after the flags
 
 struct b200_graph {
     cudaGraphExec_t exec = nullptr;

@@ -4,6 +4,7 @@
     python -m juliavision_b200.microbench attention --batch 1 --heads 12 --seq 4096 --head-dim 64
     python -m juliavision_b200.microbench layernorm --groups 65536 --channels 1280
     python -m juliavision_b200.microbench hiera --batch 1          # whole image-encoder pass, eager launches
+    python -m juliavision_b200.microbench gemv --features 51865 --k 1280 [--dtype float32]
 
 Each run warms up, then times `reps` back-to-back calls over `--buffers` rotating operand sets
 (so L2 does not keep one set resident) and prints one JSON line.  With `--reps` small this is also
@@ -84,6 +85,27 @@ def layernorm(ctx, a):
     return dict(op="layernorm", groups=a.groups, channels=a.channels, ms=round(ms, 5), gbs=round(nbytes / ms / 1e6, 1))
 
 
+def gemv(ctx, a):
+    rng = np.random.default_rng(a.seed)
+    dt = np.dtype(a.dtype).type
+    sets = []
+    for _ in range(a.buffers):
+        W = ctx.toback((rng.standard_normal((a.k, a.features), dtype=np.float32) * 0.05).astype(dt))
+        x = ctx.toback(rng.standard_normal((1, a.k), dtype=np.float32).astype(dt))
+        sets.append((W, x, ctx.allocate(dt, a.features, 1)))
+    i = [0]
+
+    def go():
+        W, x, o = sets[i[0] % a.buffers]
+        i[0] += 1
+        ctx.ws.reset()
+        jv.matmul_(ctx, o, W, x, None)
+
+    ms = _time(ctx, go, a.reps)
+    nbytes = a.features * a.k * np.dtype(dt).itemsize
+    return dict(op="gemv", features=a.features, k=a.k, dtype=a.dtype, ms=round(ms, 5), gbs=round(nbytes / ms / 1e6, 1))
+
+
 def hiera(ctx, a):
     from .hiera import Hiera, HieraConfig
     cfg = HieraConfig()
@@ -114,14 +136,18 @@ def main():
     ln.add_argument("--channels", type=int, default=1280)
     hi = sub.add_parser("hiera")
     hi.add_argument("--batch", type=int, default=1)
-    for s in (g, at, ln, hi):
+    gv = sub.add_parser("gemv")
+    gv.add_argument("--features", type=int, default=51865)
+    gv.add_argument("--k", type=int, default=1280)
+    gv.add_argument("--dtype", default="float16", choices=["float16", "float32"])
+    for s in (g, at, ln, hi, gv):
         s.add_argument("--reps", type=int, default=20)
         s.add_argument("--buffers", type=int, default=3)
         s.add_argument("--seed", type=int, default=0)
         s.add_argument("--device", type=int, default=0)
     a = ap.parse_args()
     with jv.Ctx(a.device) as ctx:
-        print(json.dumps({"gemm": gemm, "attention": attention, "layernorm": layernorm, "hiera": hiera}[a.op](ctx, a)), flush=True)
+        print(json.dumps({"gemm": gemm, "attention": attention, "layernorm": layernorm, "hiera": hiera, "gemv": gemv}[a.op](ctx, a)), flush=True)
 
 
 if __name__ == "__main__":

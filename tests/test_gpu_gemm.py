@@ -202,6 +202,11 @@ def test_gemv_one_token(ctx, ora, dtype, M, K):
         jv.matmul_(ctx, out, A, B, bb, epi=epi)
         ctx.synchronize()
         got = out.to_host()
+        ctx.fill_bytes(out, 0xFF)
+        ctx.ws.reset()
+        jv.matmul_(ctx, out, A, B, bb, epi=epi)      # the K split's partial sums are added in a fixed order
+        ctx.synchronize()
+        assert np.array_equal(got.view(np.uint8), out.to_host().view(np.uint8))
         want = x.astype(np.float64) @ Wt.astype(np.float64) + (b.astype(np.float64) if bb is not None else 0)
         if dtype == np.float16:
             ref = ora.linear(x, Wt, b if bb is not None else None, epi=epi if epi != "identity" else "none")
@@ -210,6 +215,31 @@ def test_gemv_one_token(ctx, ora, dtype, M, K):
             from scipy.special import erf
             ref = {"identity": want, "relu": np.maximum(want, 0), "gelu": 0.5 * want * (1 + erf(want / np.sqrt(2)))}[epi]
             assert relerr(got, ref) < 1e-4, describe(got, ref, 1e-4)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("M0,lead,rows", [(3, 1000, 251), (1, 264, 1), (5, 4099, 4000), (0, 496, 496), (7, 249, 242)])
+def test_gemv_rows_of_a_wider_matrix(ctx, dtype, M0, lead, rows):
+    """A is rows M0 .. M0+rows of a (lead, K) matrix: the first element off a 16-byte boundary and a
+    leading dimension of any parity, so every column starts at its own offset within an aligned vector.
+    The rows outside the view hold huge values, which must not reach the result."""
+    K = 300
+    rng = np.random.default_rng(lead + rows)
+    full = np.full((K, lead), 6.0e4, dtype)                         # torch (in, out): column-major (lead, K)
+    full[:, M0:M0 + rows] = (rng.standard_normal((K, rows)) * 0.05).astype(dtype)
+    x = rng.standard_normal((1, K)).astype(dtype)
+    A = ctx.toback(full).slice(0, M0, M0 + rows)
+    B = ctx.toback(x)
+    out = ctx.allocate(np.float32, rows, 1)
+    ctx.fill_bytes(out, 0xFF)
+    assert isinstance(jv.mmplan(ctx, out, A, B, None), jv.MMGemvPlan)
+    ctx.ws.reset()
+    jv.matmul_(ctx, out, A, B, None)
+    ctx.synchronize()
+    got = out.to_host().reshape(-1)
+    want = (x.astype(np.float64) @ full[:, M0:M0 + rows].astype(np.float64)).reshape(-1)
+    assert np.all(np.isfinite(got))
+    assert relerr(got, want) < 1e-4, describe(got, want, 1e-4)
 
 
 def test_timeline_records_time_and_cycles(ctx):
