@@ -144,8 +144,10 @@ int b200_gemm_f16_plan(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t n
 /* The one-token product of matmul! (MMGemvPlan + Lava.gemv!, matmul.jl:103-137):
  * out[m] = epi(T(bias[m] + sum_k A[m,k] x[k])), A (M,K) column-major with leading dimension lda
  * (M contiguous), x (K), bias (M) or NULL, all of in_dtype (B200_F32 as in the reference, or
- * B200_F16); out (M) of out_dtype (fp32, or fp16 for fp16 operands); fp32 accumulation.  Scratch for
- * a split along K comes from the context workspace. */
+ * B200_F16); out (M) of out_dtype (fp32, or fp16 for fp16 operands); fp32 accumulation.  Any lda >= M
+ * and any element-aligned A are read as aligned 16-byte vectors, which may include the other bytes of
+ * the 16-byte blocks the array's first and last elements sit in.  Scratch for a split along K comes from
+ * the context workspace. */
 int b200_gemv(b200_ctx* ctx, int64_t M, int64_t K, const void* A, int64_t lda, const void* x,
               const void* bias, int in_dtype, void* out, int out_dtype, int epilogue);
 
