@@ -752,6 +752,10 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
                                        ATT_SMEM_BYTES));
         attr_done[ctx->device & 15] = true;
     }
+    // Many windows of at most 64 keys: bound by HBM and latency, not by the tensor pipe; the small-tile
+    // kernel keeps eight CTAs per SM in flight where this one's set-up would cost more than the arithmetic.
+    if (bptr == nullptr && Lk <= 64 && B * H * cdiv(Lq, 64) > 2 * ctx->prop.multiProcessorCount)
+        return attention_window_launch(ctx, E, Lq, Lk, H, B, q, k, v, o, out_dtype, scale);
     // Many short sequences (attention windows of a few dozen tokens) would each occupy a CTA whose
     // 128-row tiles are mostly empty.  When consecutive sequences are also consecutive in memory —
     // batch stride = L x token stride in q, k, v and out — g of them are run as one sequence of g x L

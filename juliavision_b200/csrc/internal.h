@@ -84,6 +84,12 @@ int pool_alloc(b200_ctx* ctx, size_t bytes, void** out);
 int pool_free(b200_ctx* ctx, void* p);
 int ws_scratch(b200_ctx* ctx, size_t bytes, void** out);
 
+// Attention over windows of at most 64 keys, E <= 64 (attention_window.cu).  Operands as the tensor-core
+// path wants them: E contiguous, 16-byte aligned pointers and strides.
+int attention_window_launch(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B, const b200_strided4* q,
+                            const b200_strided4* k, const b200_strided4* v, const b200_strided4* o, int out_dtype,
+                            float scale);
+
 // GEMM with the bias broadcast along either axis (bias_per_n = 1: one value per column j,
 // which is what a convolution lowered to a GEMM over pixels needs).
 int gemm_f16_run(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,

@@ -169,12 +169,13 @@ def test_config2_sample_rows_vs_oracle(ctx, ora):
     assert relerr(got[:, :, rows], ref) < TOL, describe(got[:, :, rows], ref, TOL)
 
 
-@pytest.mark.parametrize("B,H,Lq,Lk,E", [(512, 2, 64, 64, 56), (1024, 4, 16, 64, 56), (300, 2, 64, 64, 64), (256, 2, 49, 49, 32)])
-def test_many_small_windows_packed(ctx, ora, B, H, Lq, Lk, E):
+@pytest.mark.parametrize("B,H,Lq,Lk,E", [(512, 2, 64, 64, 56), (1024, 4, 16, 64, 56), (300, 2, 64, 64, 64), (256, 2, 49, 49, 32),
+                                         (200, 3, 100, 40, 8), (400, 1, 1, 64, 16), (310, 1, 23, 1, 24), (150, 2, 129, 64, 48)])
+def test_many_small_windows(ctx, ora, B, H, Lq, Lk, E):
     """Attention windows of a few dozen tokens, token-major with the windows back to back (what the image
-    encoder hands over): the library runs several windows as one sequence under a block-diagonal mask.
-    Values must be those of independent windows: checked against the oracle window by window, and a
-    window's result must not change when its neighbours do."""
+    encoder hands over): many of them take the small-tile kernel (64 queries of one window and head per
+    CTA).  Values must be those of independent windows: checked against the oracle window by window, and
+    a window's result must not change when its neighbours do."""
     from .gpu_helpers import qkv_views
     rng = np.random.default_rng(B + Lq + Lk)
     qb = np.float16(rng.standard_normal((B, Lq, H, E)))
@@ -201,6 +202,26 @@ def test_many_small_windows_packed(ctx, ora, B, H, Lq, Lk, E):
     vb2[1::2] = 7
     got2 = run(q, kb2.transpose(0, 2, 1, 3), vb2.transpose(0, 2, 1, 3))
     assert np.array_equal(got2[0::2], got[0::2])
+
+
+@pytest.mark.parametrize("B,H,Lq,Lk,E", [(512, 2, 64, 64, 56), (300, 1, 70, 33, 40)])
+def test_many_small_windows_dense_fp32_out(ctx, ora, B, H, Lq, Lk, E):
+    """The same windows from dense (B,H,L,E) arrays into an fp32 result (the attn_flash! contract)."""
+    from .gpu_helpers import qkv_views
+    rng = np.random.default_rng(B + Lq + Lk + 1)
+    q = np.float16(rng.standard_normal((B, H, Lq, E)))
+    k = np.float16(rng.standard_normal((B, H, Lk, E)))
+    v = np.float16(rng.standard_normal((B, H, Lk, E)))
+    scale = 1 / np.sqrt(E)
+    dq, dk, dv = qkv_views(ctx, q, k, v)
+    out = ctx.allocate(np.float32, E, Lq, H, B)
+    ctx.fill_bytes(out, 0xFF)
+    jv.sdpa(ctx, dq, dk, dv, None, scale, out=out)
+    ctx.synchronize()
+    got = out.to_host()
+    ref = ora.attention_ref(q, k, v, scale)
+    assert np.all(np.isfinite(got))
+    assert relerr(got, ref) < TOL, describe(got, ref, TOL)
 
 
 @pytest.mark.parametrize("B,H,Lq,Lk,E", [(1, 8, 23, 4096, 64), (2, 3, 1, 4000, 56), (1, 1, 300, 2048, 32), (1, 20, 130, 1500, 64),
