@@ -170,7 +170,8 @@ def test_config2_sample_rows_vs_oracle(ctx, ora):
 
 
 @pytest.mark.parametrize("B,H,Lq,Lk,E", [(512, 2, 64, 64, 56), (1024, 4, 16, 64, 56), (300, 2, 64, 64, 64), (256, 2, 49, 49, 32),
-                                         (200, 3, 100, 40, 8), (400, 1, 1, 64, 16), (310, 1, 23, 1, 24), (150, 2, 129, 64, 48)])
+                                         (200, 3, 100, 40, 8), (400, 1, 1, 64, 16), (310, 1, 23, 1, 24), (150, 2, 129, 64, 48),
+                                         (16, 8, 256, 256, 56), (40, 2, 64, 256, 56), (64, 3, 130, 200, 64), (90, 2, 17, 65, 16)])
 def test_many_small_windows(ctx, ora, B, H, Lq, Lk, E):
     """Attention windows of a few dozen tokens, token-major with the windows back to back (what the image
     encoder hands over): many of them take the small-tile kernel (64 queries of one window and head per
