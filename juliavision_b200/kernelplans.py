@@ -45,7 +45,10 @@ class MMGemvPlan:
 @dataclass(frozen=True)
 class FlashTCPlan:
     """Fused single-pass attention on tcgen05; stands where FlashCMPlan stood
-    (kernelplans.jl:54-324). BR/BC are the query/key block, EP the padded head dim."""
+    (kernelplans.jl:54-324). BR/BC are the query/key block, EP the padded head dim.  Holding this
+    plan means the call runs; inside it the library still chooses how: whole query-tile pairs, a key
+    split with a merge for few queries over many keys, and for many windows of at most 64 keys a
+    small-tile kernel (64 queries of one window and head per CTA) instead of the 128-row tiles."""
     BR: int = 128
     BC: int = 128
     EP: int = 64
