@@ -36,6 +36,13 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const __half* row) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
@@ -89,23 +96,22 @@ __global__ void __launch_bounds__(AW_THREADS, 6) attention_window_kernel(const W
     if (r0 >= qrows) return;
 
     // S = Q K^T: 16 queries x 64 keys as eight n-tiles of 8 keys, four k-steps of 16 along E
+    // Fragments come out of the row-major tiles with ldmatrix: four 8 x 8 blocks per instruction.
     uint32_t qa[4][4];
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-        const __half* a = Qs + (r0 + g) * AW_PITCH + ks * 16 + 2 * t;
-        qa[ks][0] = *reinterpret_cast<const uint32_t*>(a);
-        qa[ks][1] = *reinterpret_cast<const uint32_t*>(a + 8 * AW_PITCH);
-        qa[ks][2] = *reinterpret_cast<const uint32_t*>(a + 8);
-        qa[ks][3] = *reinterpret_cast<const uint32_t*>(a + 8 * AW_PITCH + 8);
-    }
+    for (int ks = 0; ks < 4; ++ks)      // blocks (rows 0-7 | 8-15) x (dims 16ks.. | 16ks+8..) of the warp's queries
+        ldmatrix_x4(qa[ks], Qs + (r0 + (lane & 7) + ((lane >> 3) & 1) * 8) * AW_PITCH + ks * 16 + (lane >> 4) * 8);
     float s[8][4];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 8; nt += 2) {
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-            const __half* kb = Ks + (nt * 8 + g) * AW_PITCH + ks * 16 + 2 * t;
-            mma_16816(s[nt], qa[ks], *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
+            uint32_t kb[4];             // blocks (keys 8nt.. | 8nt+8..) x (dims 16ks.. | 16ks+8..)
+            ldmatrix_x4(kb, Ks + ((nt + (lane >> 4)) * 8 + (lane & 7)) * AW_PITCH + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma_16816(s[nt], qa[ks], kb[0], kb[1]);
+            mma_16816(s[nt + 1], qa[ks], kb[2], kb[3]);
         }
     }
     // softmax over the keys of rows g (values 0,1) and g + 8 (values 2,3); a quad of lanes shares a row
