@@ -59,9 +59,6 @@ struct AttnParams {
     const __half* bias;
     int64_t bsK, bsQ, bsH, bsB;
     int bias_vec;
-    // Several short sequences packed into one (set by the host when windows are small): query i may
-    // only see the keys of its own window, i / dq == key / dk.  0 = no packing.
-    int dq, dk;
     // Keys split over nsplit CTAs per query pair (few queries, many keys): each writes its unnormalised
     // fp32 O rows to part_o[split][tail pair][256 rows][E] and (reference point, row sum) to part_ml[...][2];
     // attention_merge_kernel combines them (the reference's attn_flash_cm_merge!, flash.jl:1398-1421).
@@ -100,9 +97,8 @@ __device__ __forceinline__ void tmem_st16_raw(uint32_t taddr, const uint32_t* r)
 //              other tile's softmax runs
 // P never touches shared memory: the softmax threads write it as packed fp16 into tensor memory and
 // the P V product takes its A operand from there, so the shared-memory port only feeds K and V.
-// BIAS: the scaled score gets an additive fp16 mask before the softmax and/or the block-diagonal mask
-// of packed windows; a row whose keys are all blocked (-inf everywhere) comes out as zeros, as in
-// attn_softmax (attention.jl:73-100).
+// BIAS: the scaled score gets an additive fp16 mask before the softmax; a row whose keys are all
+// blocked (-inf everywhere) comes out as zeros, as in attn_softmax (attention.jl:73-100).
 template <bool BIAS>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
@@ -351,15 +347,6 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                                     r[c][i] = __float_as_uint(fmaf(__uint_as_float(r[c][i]), sc, bv * L2E));
                                 }
                         }
-                    }
-                    if (p.dq > 0) {
-                        // packed windows: only the keys [lo, hi) of this block belong to this row's window
-                        const int lo = (lq / p.dq) * p.dk - (jb0 + j) * ATT_BC, hi = lo + p.dk;
-#pragma unroll
-                        for (int c = 0; c < 4; ++c)
-#pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (c * 32 + i < lo || c * 32 + i >= hi) r[c][i] = 0xff800000u;
                     }
                 }
                 // Row maximum of the raw scores (the scale is positive, so it commutes with max);
@@ -753,29 +740,9 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
         attr_done[ctx->device & 15] = true;
     }
     // Many windows of at most 64 keys: bound by HBM and latency, not by the tensor pipe; the small-tile
-    // kernel keeps eight CTAs per SM in flight where this one's set-up would cost more than the arithmetic.
+    // kernel keeps six CTAs per SM in flight where this one's set-up would cost more than the arithmetic.
     if (bptr == nullptr && Lk <= 64 && B * H * cdiv(Lq, 64) > 2 * ctx->prop.multiProcessorCount)
         return attention_window_launch(ctx, E, Lq, Lk, H, B, q, k, v, o, out_dtype, scale);
-    // Many short sequences (attention windows of a few dozen tokens) would each occupy a CTA whose
-    // 128-row tiles are mostly empty.  When consecutive sequences are also consecutive in memory —
-    // batch stride = L x token stride in q, k, v and out — g of them are run as one sequence of g x L
-    // with a block-diagonal mask: fewer, fuller CTAs, the same values.
-    b200_strided4 qm = *q, km = *k, vm = *v, om = *o;
-    int pack_dq = 0, pack_dk = 0;
-    if (bptr == nullptr && Lk <= 64 && Lq <= Lk && B >= 4 && B * H * cdiv(Lq, 2 * ATT_BR) > 2 * ctx->prop.multiProcessorCount) {
-        auto packed = [&](const b200_strided4* t, int64_t L) { return L == 1 || t->stride[3] == L * t->stride[1]; };
-        if (packed(q, Lq) && packed(k, Lk) && packed(v, Lk) && packed(o, Lq)) {
-            int64_t g = 1;
-            while (B % (2 * g) == 0 && 2 * g * Lq <= 2 * ATT_BR && 2 * g * Lk <= 4 * ATT_BC) g *= 2;
-            if (g > 1) {
-                pack_dq = (int)Lq;
-                pack_dk = (int)Lk;
-                qm.stride[3] *= g; km.stride[3] *= g; vm.stride[3] *= g; om.stride[3] *= g;
-                Lq *= g; Lk *= g; B /= g;
-            }
-        }
-    }
-    q = &qm; k = &km; v = &vm; o = &om;
     CUtensorMap tq, tk, tv;
     int rc;
     if ((rc = make_qkv_map(ctx, &tq, q, E, Lq, H, B))) return rc;
@@ -792,8 +759,6 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
     p.bias = bptr;
     p.bsK = bs[0]; p.bsQ = bs[1]; p.bsH = bs[2]; p.bsB = bs[3];
     p.bias_vec = bptr && bs[0] == 1 && al16(bptr) && bs[1] % 8 == 0 && bs[2] % 8 == 0 && bs[3] % 8 == 0;
-    p.dq = pack_dq;
-    p.dk = pack_dk;
     p.qpairs = (int)cdiv(Lq, 2 * ATT_BR);
     const int64_t pairs = (int64_t)p.qpairs * H * B;
     B200_REQUIRE(pairs < (1ll << 30), B200_DECLINE_EXTENT, "attention: too many query tiles");
@@ -807,7 +772,7 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
     p.part_o = p.part_ml = nullptr;
     const int64_t nblk_all = cdiv(Lk, ATT_BC);
     const int64_t rem = pairs % sms;
-    if (bptr == nullptr && pack_dq == 0 && nblk_all >= 4) {
+    if (bptr == nullptr && nblk_all >= 4) {
         int64_t ntail = 0, ns = 1;
         if (2 * pairs <= sms) {
             ntail = pairs;
@@ -846,7 +811,7 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
     int64_t nsplit = (pairs > sms && rem > 0 && 2 * rem <= sms && Lq % (2 * ATT_BR) == 0) ? rem : 0;
     p.pair_ctas = (int)(pairs - nsplit);
     dim3 grid((unsigned)(pairs + nsplit), 1, 1);
-    if (bptr || p.dq > 0)
+    if (bptr)
         B200_CUDA(launch_dep(attention_f16_tc_kernel<true>, grid, dim3(ATT_THREADS, 1, 1), ATT_SMEM_BYTES, ctx->stream, 1,
                              tq, tk, tv, p));
     else
