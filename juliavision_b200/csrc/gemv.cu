@@ -155,8 +155,8 @@ static int gemv_run(b200_ctx* ctx, int64_t M, int64_t K, const void* A, int64_t 
     const int64_t maxsplit = K / (GEMV_MIN_COLS * GEMV_WARPS) > 0 ? K / (GEMV_MIN_COLS * GEMV_WARPS) : 1;
     if (ksplit > maxsplit) ksplit = maxsplit;
     if (ksplit > 64) ksplit = 64;
-    const int64_t kchunk = cdiv(K, ksplit);
-    ksplit = cdiv(K, kchunk);
+    const int64_t kchunk = K > 0 ? cdiv(K, ksplit) : 1;   // K = 0: one block per row range writes the bias
+    ksplit = K > 0 ? cdiv(K, kchunk) : 1;
     float* partial = nullptr;
     if (ksplit > 1) {
         void* ws = nullptr;

@@ -242,6 +242,21 @@ def test_gemv_rows_of_a_wider_matrix(ctx, dtype, M0, lead, rows):
     assert relerr(got, want) < 1e-4, describe(got, want, 1e-4)
 
 
+def test_gemv_without_a_reduction_axis(ctx):
+    """K = 0 through the C ABI: the sum is empty, the result is the bias (or zero)."""
+    import ctypes as C
+    from juliavision_b200 import _lib
+    M = 300
+    b = np.float16(np.random.default_rng(3).standard_normal(M))
+    bias, out = ctx.toback(b), ctx.allocate(np.float16, M, 1)
+    for bp, want in ((bias.ptr, b), (None, np.zeros(M, np.float16))):
+        ctx.fill_bytes(out, 0xFF)
+        rc = _lib.lib().b200_gemv(ctx.handle, M, 0, None, M, None, bp, _lib.F16, out.ptr, _lib.F16, 0)
+        assert rc == _lib.OK
+        ctx.synchronize()
+        assert np.array_equal(out.to_host().reshape(-1), want)
+
+
 def test_timeline_records_time_and_cycles(ctx):
     """b200_timeline: worker 0's events in nanoseconds and in SM cycles; their ratio is a plausible clock,
     the events are in order, every worker's exit is recorded, and nothing is written once it is off."""
