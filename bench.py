@@ -46,8 +46,10 @@ def peaks():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch of the config-3 pass, mean over its 128
-# launches, from the profiler capture summarised in profiles/gemm_f16_tc_encoder_pass_dram_traffic.md.
+# launches, from one profiler capture of that pass (a profiler cannot run inside a timed benchmark, so
+# the figure is carried as a constant; GEMM_DRAM_CAPTURE says which kernel version it was taken from).
 GEMM_DRAM_BYTES_PER_LAUNCH = 16_627_000
+GEMM_DRAM_CAPTURE = "ncu, one encoder pass, GEMM kernel as of 2026-11-25 (whole-tile schedule, 256x256 pair tiles)"
 
 
 class ClockSampler:
@@ -277,47 +279,78 @@ def kernel_figures(ctx, jv, pk, quick: bool):
     return out
 
 
-def cpu_baseline(cfg, weights, x, layers: int):
-    """The oracle's encoder on the host cores: `layers` of the stack, extrapolated linearly."""
+def cpu_baseline(ctx, cfg, weights, x, layers: int):
+    """The oracle's encoder on the host cores: `layers` of the stack, extrapolated linearly.  Its output
+    (the residual stream after `layers` layers) also checks the GPU's same prefix on the same input."""
+    from juliavision_b200.encoder import Encoder, EncoderConfig
     from oracle import oracle as ora
     from oracle.encoder_ref import oracle_forward
+    cores = ora.use_all_cores()
     t0 = time.perf_counter()
-    oracle_forward(cfg, weights, x, layers=layers)
+    ref = oracle_forward(cfg, weights, x, layers=layers)
     dt = time.perf_counter() - t0
     ms_full = dt * 1e3 * cfg.layers / layers
-    return dict(value=round(ms_full, 1), unit=UNIT, cores=ora.num_threads(), kind="port",
+    base = dict(value=round(ms_full, 1), unit=UNIT, cores=cores, kind="port",
                 sample=f"{layers} of {cfg.layers} layers of the same encoder on the same input ({dt:.1f} s), "
                        f"extrapolated linearly to {cfg.layers} layers")
+    import dataclasses
+    pcfg = dataclasses.replace(cfg, layers=layers)
+    prefix = Encoder(ctx, pcfg, weights[:layers] + [weights[-1]])
+    ctx.upload(prefix.xin, x)
+    prefix.forward()
+    ctx.synchronize()
+    got = prefix.x.to_host().astype(np.float64)
+    ref = ref.astype(np.float64)
+    rel = float(np.max(np.abs(got - ref)) / np.max(np.abs(ref)))
+    parity = dict(layers=layers, rel_err=round(rel, 6), tol=1e-2, ok=bool(rel < 1e-2),
+                  what=f"residual stream after {layers} layers, this library against the CPU oracle, same input and weights, "
+                       "max|d|/max|ref|")
+    return base, parity
+
+
+def workload_name(cfg) -> str:
+    """The one description of the timed workload, shared by both arms so their lines compare."""
+    return (f"config 3: {cfg.layers}-layer pre-LN encoder, d_model {cfg.d_model}, {cfg.heads} heads, "
+            f"FFN {cfg.ffn} GELU, {cfg.tokens}x{cfg.d_model} input, batch 1 per GPU")
+
+
+REFERENCE_LAYERS_PER_STEP = 1
 
 
 def run_reference(args):
-    """The reference's CPU form of the path (C oracle; the Julia original cannot run here)."""
+    """The reference's CPU form of the path (C oracle; the Julia original cannot run here) on every host
+    core this process may use.  A step is a bounded sample of the workload: REFERENCE_LAYERS_PER_STEP of the
+    32 identical layers at the full geometry (about a second on 16 cores), so that --steps K --warmup W are
+    honoured as given; `ms_per_step` is the measured time of that sampled step and `value` its linear
+    extrapolation to the whole stack."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from juliavision_b200.encoder import EncoderConfig, init_weights
-    cfg = EncoderConfig()
-    layers = 4
-    weights = init_weights(EncoderConfig(layers=layers)) + []
-    x = np.float16(np.random.default_rng(11).standard_normal((cfg.tokens, cfg.d_model), dtype=np.float32))
     from oracle import oracle as ora
     from oracle.encoder_ref import oracle_forward
-    wl = weights[:layers] + [weights[-1]]
-    for _ in range(min(args.warmup, 1)):
+    cores = ora.use_all_cores()      # a one-process-per-GPU launcher exports OMP_NUM_THREADS=1: not wanted here
+    cfg = EncoderConfig(layers=args.layers)
+    layers = min(REFERENCE_LAYERS_PER_STEP, cfg.layers)
+    wl = init_weights(EncoderConfig(layers=layers))
+    x = np.float16(np.random.default_rng(11).standard_normal((cfg.tokens, cfg.d_model), dtype=np.float32))
+    for _ in range(args.warmup):
         oracle_forward(cfg, wl, x, layers=layers)
     times = []
-    for _ in range(max(1, min(args.steps, 3))):
+    for _ in range(args.steps):
         t0 = time.perf_counter()
         oracle_forward(cfg, wl, x, layers=layers)
         times.append(time.perf_counter() - t0)
-    ms = float(np.mean(times)) * 1e3 * cfg.layers / layers
-    line = dict(impl="reference", metric=METRIC, value=round(ms, 1), unit=UNIT, n_gpus=args.gpus, steps=len(times),
-                warmup=min(args.warmup, 1), ms_per_step=round(ms, 1), higher_is_better=False, scaling="weak",
+    ms_step = float(np.mean(times)) * 1e3
+    ms = ms_step * cfg.layers / layers
+    sample = (f"each step = {layers} of {cfg.layers} layers at the full geometry (measured {ms_step:.1f} ms per step); "
+              f"value = that time x {cfg.layers // layers}, the layers being identical in cost")
+    line = dict(impl="reference", metric=METRIC, value=round(ms, 1), unit=UNIT, n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=round(ms_step, 2), higher_is_better=False, scaling="weak",
                 vs_baseline=None, dtype="f16 (fp32 accumulate)", data="synthetic",
-                config=dict(workload="config 3: 32-layer pre-LN encoder, d_model 1280, 20 heads, FFN 5120 GELU, "
-                                     "1500x1280 input, batch 1"),
-                cpu_baseline=dict(value=round(ms, 1), unit=UNIT, cores=ora.num_threads(), kind="port",
-                                  sample=f"each step = {layers} of {cfg.layers} layers, extrapolated linearly"),
+                config=dict(workload=workload_name(cfg)), layers_timed=layers,
+                value_extrapolated_from=f"{layers} of {cfg.layers} layers",
+                cpu_baseline=dict(value=round(ms, 1), unit=UNIT, cores=cores, kind="port", sample=sample),
                 e2e=dict(value=round(ms, 1), unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
 
@@ -541,17 +574,16 @@ def main():
     kernels = None
     if rank == 0 and world == 1 and not args.no_kernels:
         kernels = kernel_figures(ctx, jv, pk, quick=args.steps < 10)
-    cpu = None
+    cpu = parity = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        cpu = cpu_baseline(cfg, weights, x, min(args.cpu_layers, cfg.layers))
+        cpu, parity = cpu_baseline(ctx, cfg, weights, x, min(args.cpu_layers, cfg.layers))
 
     if rank == 0:
         line = dict(
             metric=METRIC, value=round(ms_step / world, 4), unit=UNIT, n_gpus=world, steps=args.steps, warmup=warmup,
             ms_per_step=round(ms_step, 4), higher_is_better=False, scaling="weak", vs_baseline=None,
             dtype="f16 (fp32 accumulate)", data="synthetic",
-            config=dict(workload=f"config 3: {cfg.layers}-layer pre-LN encoder, d_model {cfg.d_model}, {cfg.heads} heads, "
-                                 f"FFN {cfg.ffn} GELU, {cfg.tokens}x{cfg.d_model} input, batch 1 per GPU",
+            config=dict(workload=workload_name(cfg),
                         parallelism=f"batch-sharded x{world}, weights replicated, no collective",
                         l2="inputs larger than L2: each pass streams 1.18 GB of weights", replay="cuda graph",
                         imgs_per_step=world, tflops_per_gpu=round(cfg.flops() / ms_step / 1e9, 1)),
@@ -564,11 +596,11 @@ def main():
                           avg_launch_ms=round(gemm_ms / n_gemm, 5), traffic=GEMM_DRAM_BYTES_PER_LAUNCH,
                           traffic_unit="bytes per launch (dram read + write, mean over the 128 launches of a pass)",
                           algorithmic_bytes=round(gemm_bytes / n_gemm),
+                          traffic_from_capture=GEMM_DRAM_CAPTURE,
                           note="all GEMM launches of one pass, replayed back to back; flops = 2MNK unpadded; "
-                               "traffic from the profiler capture summarised in "
-                               "profiles/gemm_f16_tc_encoder_pass_dram_traffic.md (caches flushed before each "
-                               "launch there, so activations count as DRAM reads and the outputs stay in L2)"),
-            clocks=clocks, kernels=kernels, cpu_baseline=cpu)
+                               "traffic is a profiler capture (caches flushed before each launch there, so "
+                               "activations count as DRAM reads and the outputs stay in L2)"),
+            clocks=clocks, kernels=kernels, cpu_baseline=cpu, parity=parity)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

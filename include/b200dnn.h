@@ -74,6 +74,12 @@ void* b200_stream(b200_ctx* ctx); /* the cudaStream_t the context launches on   
 /* Number of kernels this library has launched on the context since creation.       */
 int64_t b200_launch_count(b200_ctx* ctx);
 
+/* Self-test of the bounded waits (no reference counterpart): launches one warp that waits, with a limit
+ * of limit_ns (at most 100 ms), on a barrier nothing ever arrives at.  The wait runs out, the kernel
+ * returns normally, and the next b200_sync reports B200_EKERNEL and clears the status, after which the
+ * context works as before.  gave_up_dev (device int, may be NULL) receives 1 when the wait gave up. */
+int b200_selftest_bounded_wait(b200_ctx* ctx, int64_t limit_ns, int* gave_up_dev);
+
 /* CUDA-event timer on the context's stream (Diagnostics.optimes, context.jl:162-221). */
 int b200_timer_start(b200_ctx* ctx);
 int b200_timer_stop(b200_ctx* ctx, float* ms_out); /* records, synchronises, reads */
@@ -82,7 +88,11 @@ int b200_timer_stop(b200_ctx* ctx, float* ms_out); /* records, synchronises, rea
  * everything launched on the context between begin and end is recorded into a CUDA graph
  * instead of running; replay launches the whole sequence with one call.  The static slab and
  * the warmed-up workspace make every device address repeat, which is the precondition.  Run
- * the sequence once eagerly first: the pool must not need cudaMalloc while capturing. */
+ * the sequence once eagerly first: the pool must not need cudaMalloc while capturing.
+ * A graph bakes device addresses into its launches.  Pool blocks handed out and workspace blocks used
+ * while capturing stay out of circulation until the graph is destroyed (a b200_pool_free of one is
+ * honoured then), so later allocations and workspace growth cannot receive memory a replay still
+ * writes.  Every caller-owned buffer the captured calls were given must outlive the graph as well. */
 typedef struct b200_graph b200_graph;
 int b200_graph_begin(b200_ctx* ctx);
 int b200_graph_end(b200_ctx* ctx, b200_graph** out);
@@ -155,8 +165,8 @@ int b200_gemv(b200_ctx* ctx, int64_t M, int64_t K, const void* A, int64_t lda, c
  * every GEMM launch records a timeline into it — globaltimer nanoseconds at [slot] and the SM's cycle
  * counter at [64 + slot]; slots: 0 entry, 1 set-up done, 3 first operand stage landed, 4.. all UMMAs
  * of the worker's tile 0, 1, 2, 3+ issued, 8.. their accumulators complete, 12.. their epilogues
- * done, 16 exit; [128 + w] is the time worker w (w < 120) left.  NULL stops it.  bench.py reads the SM
- * clock inside the main loop from it. */
+ * done, 16 exit; [128 + w] is the time worker w (w < 120) left.  NULL stops it.  The ratio of the two
+ * clocks over the main loop gives the SM clock the kernel really ran at. */
 int b200_timeline(b200_ctx* ctx, void* dptr);
 
 /* -------------------------------------------------------------------- attention */

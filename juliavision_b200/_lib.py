@@ -51,6 +51,7 @@ SIGNATURES = {
     "b200_version": (C.c_char_p, []),
     "b200_stream": (_vp, [_vp]),
     "b200_launch_count": (_i64, [_vp]),
+    "b200_selftest_bounded_wait": (_i32, [_vp, _i64, _vp]),
     "b200_timer_start": (_i32, [_vp]),
     "b200_timer_stop": (_i32, [_vp, C.POINTER(_f32)]),
     "b200_graph_begin": (_i32, [_vp]),

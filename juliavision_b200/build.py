@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(CSRC, "libb200dnn.so")
-SOURCES = ["ctx.cu", "layernorm.cu", "gemm.cu", "attention.cu", "glue.cu", "conv.cu", "gemv.cu", "attention_window.cu"]
+SOURCES = ["ctx.cu", "layernorm.cu", "gemm.cu", "attention.cu", "glue.cu", "conv.cu", "gemv.cu", "attention_window.cu", "selftest.cu"]
 HEADERS = ["internal.h", "ptx.cuh", "act.cuh", os.path.join("..", "..", "include", "b200dnn.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [

@@ -236,14 +236,16 @@ int b200_conv2d_f16_noalloc(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, in
         void* on = (char*)out + (size_t)(n * P * Cout) * osz;
         if (onebyone) {
             const __half* xa = (const __half*)x + n * P * Cin;
-            if ((rc = gemm_f16_run(ctx, P, Cout, Cin, xa, P, wB, ldwB, bias, 1, on, P, out_dtype, epilogue, 1, 0, 0, 0)))
+            if ((rc = gemm_f16_run(ctx, P, Cout, Cin, xa, P, wB, ldwB, bias, 1, on, P, out_dtype, epilogue, 1, 0, 0, 0,
+                                   /*use_workspace=*/0)))
                 return rc;
             continue;
         }
         // The gather writes all MP x CRS entries, zeros included: no clearing pass is needed.
         const __half* xn = (const __half*)x + n * W * H * Cin;
         if ((rc = b200_im2col_f16(ctx, W, H, Cin, 1, KW, KH, sx, sy, px, py, dx, dy, MP, CRS, xn, col))) return rc;
-        if ((rc = gemm_f16_run(ctx, P, Cout, CRS, col, MP, wB, ldwB, bias, 1, on, P, out_dtype, epilogue, 1, 0, 0, 0)))
+        if ((rc = gemm_f16_run(ctx, P, Cout, CRS, col, MP, wB, ldwB, bias, 1, on, P, out_dtype, epilogue, 1, 0, 0, 0,
+                                   /*use_workspace=*/0)))
             return rc;
     }
     return B200_OK;

@@ -46,6 +46,7 @@ int pool_alloc(b200_ctx* ctx, size_t bytes, void** out) {
         *out = it->second;
         ctx->live_blocks[it->second] = it->first;
         ctx->bytes_in_use += it->first;
+        if (ctx->capturing) ctx->capture_blocks.emplace_back(it->second, it->first);
         ctx->free_blocks.erase(it);
         return B200_OK;
     }
@@ -80,10 +81,61 @@ int pool_free(b200_ctx* ctx, void* p) {
     std::lock_guard<std::mutex> lk(ctx->mu);
     auto it = ctx->live_blocks.find(p);
     if (it == ctx->live_blocks.end()) return fail(B200_EINVAL, "pool_free: %p is not a live pool block", p);
-    ctx->free_blocks.emplace(it->second, p);
+    // A block some live graph still writes on replay must not reach another owner: it waits in
+    // `held` until the last such graph is destroyed.
+    if (ctx->pinned.count(p)) ctx->held.emplace(p, it->second);
+    else ctx->free_blocks.emplace(it->second, p);
     ctx->bytes_in_use -= it->second;
     ctx->live_blocks.erase(it);
     return B200_OK;
+}
+
+// graph_end: every block the capture touched becomes pinned by the new graph.
+static void pin_capture_blocks(b200_ctx* ctx, b200_graph* g) {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    std::unordered_set<void*> seen;
+    for (auto& bs : ctx->capture_blocks) {
+        void* p = bs.first;
+        if (!seen.insert(p).second) continue;
+        g->pins.push_back(p);
+        ctx->pinned[p]++;
+        if (ctx->live_blocks.count(p) || ctx->held.count(p)) continue;
+        // Handed out and returned while capturing: take it back out of the free list.
+        auto range = ctx->free_blocks.equal_range(bs.second);
+        for (auto it = range.first; it != range.second; ++it)
+            if (it->second == p) {
+                ctx->free_blocks.erase(it);
+                ctx->held.emplace(p, bs.second);
+                break;
+            }
+    }
+    ctx->capture_blocks.clear();
+    ctx->graphs.insert(g);
+}
+
+// graph_destroy: blocks no live graph uses any more go back into circulation.
+static void unpin_blocks(b200_graph* g) {
+    b200_ctx* ctx = g->ctx;
+    if (!ctx) return;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    for (void* p : g->pins) {
+        auto it = ctx->pinned.find(p);
+        if (it == ctx->pinned.end()) continue;
+        if (--it->second > 0) continue;
+        ctx->pinned.erase(it);
+        auto h = ctx->held.find(p);
+        if (h != ctx->held.end()) {
+            ctx->free_blocks.emplace(h->second, p);
+            ctx->held.erase(h);
+        }
+    }
+    g->pins.clear();
+    ctx->graphs.erase(g);
+}
+
+static size_t pool_block_size(b200_ctx* ctx, void* p) {   // caller holds ctx->mu
+    auto it = ctx->live_blocks.find(p);
+    return it == ctx->live_blocks.end() ? 0 : it->second;
 }
 
 int ws_scratch(b200_ctx* ctx, size_t bytes, void** out) {
@@ -105,6 +157,10 @@ int ws_scratch(b200_ctx* ctx, size_t bytes, void** out) {
     }
     ctx->ws_used = need;
     *out = static_cast<char*>(ctx->ws_buf) + off;
+    if (ctx->capturing) {
+        std::lock_guard<std::mutex> lk(ctx->mu);
+        ctx->capture_blocks.emplace_back(ctx->ws_buf, pool_block_size(ctx, ctx->ws_buf));
+    }
     return B200_OK;
 }
 
@@ -164,10 +220,13 @@ int b200_ctx_create(int device, b200_ctx** out) {
     if (e != cudaSuccess) { delete c; return fail_cuda(e, "cudaStreamCreate"); }
     e = cudaMalloc(&c->d_status, 256);
     if (e != cudaSuccess) { cudaStreamDestroy(c->stream); delete c; return fail_cuda(e, "cudaMalloc(status)"); }
-    cudaMemset(c->d_status, 0, 256);
+    cudaMemsetAsync(c->d_status, 0, 256, c->stream);
     e = cudaMalloc(&c->sk_flags, (SK_FLAG_COUNT + GEMV_COUNTER_COUNT) * sizeof(int));
     if (e != cudaSuccess) { cudaFree(c->d_status); cudaStreamDestroy(c->stream); delete c; return fail_cuda(e, "cudaMalloc(flags)"); }
-    cudaMemset(c->sk_flags, 0, (SK_FLAG_COUNT + GEMV_COUNTER_COUNT) * sizeof(int));
+    // Zeroed on the context's own stream (a non-blocking stream does not wait for the legacy default
+    // stream), and complete before the first launch can be issued.
+    cudaMemsetAsync(c->sk_flags, 0, (SK_FLAG_COUNT + GEMV_COUNTER_COUNT) * sizeof(int), c->stream);
+    cudaStreamSynchronize(c->stream);
     cudaEventCreate(&c->ev0);
     cudaEventCreate(&c->ev1);
     void* fn = nullptr;
@@ -186,8 +245,10 @@ int b200_ctx_destroy(b200_ctx* c) {
     if (!c) return B200_OK;
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
+    for (b200_graph* g : c->graphs) g->ctx = nullptr;   // a graph destroyed later has nothing left to unpin
     for (auto& kv : c->free_blocks) cudaFree(kv.second);
     for (auto& kv : c->live_blocks) cudaFree(kv.first);
+    for (auto& kv : c->held) cudaFree(kv.first);
     if (c->d_status) cudaFree(c->d_status);
     if (c->sk_flags) cudaFree(c->sk_flags);
     if (c->ev0) cudaEventDestroy(c->ev0);
@@ -219,7 +280,11 @@ int b200_sync(b200_ctx* c) {
     int st = 0;
     B200_CUDA(cudaMemcpy(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (st != 0) {
-        cudaMemset(c->d_status, 0, sizeof(int));
+        // A kernel that gave up may have left hand-off flags and arrival counters set: clear them with
+        // the status word, on the context's stream, before anything else is launched.
+        cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream);
+        cudaMemsetAsync(c->sk_flags, 0, (SK_FLAG_COUNT + GEMV_COUNTER_COUNT) * sizeof(int), c->stream);
+        cudaStreamSynchronize(c->stream);
         return fail(B200_EKERNEL, "a kernel gave up a bounded wait (device status %d)", st);
     }
     return B200_OK;
@@ -247,6 +312,7 @@ int b200_graph_begin(b200_ctx* c) {
     B200_CUDA(cudaSetDevice(c->device));
     B200_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     c->capturing = true;
+    c->capture_blocks.clear();
     return B200_OK;
 }
 int b200_graph_end(b200_ctx* c, b200_graph** out) {
@@ -258,9 +324,14 @@ int b200_graph_end(b200_ctx* c, b200_graph** out) {
     cudaGraphExec_t ex = nullptr;
     cudaError_t e = cudaGraphInstantiate(&ex, g, 0);
     cudaGraphDestroy(g);
-    if (e != cudaSuccess) return fail_cuda(e, "cudaGraphInstantiate");
+    if (e != cudaSuccess) {
+        c->capture_blocks.clear();
+        return fail_cuda(e, "cudaGraphInstantiate");
+    }
     b200_graph* r = new b200_graph();
     r->exec = ex;
+    r->ctx = c;
+    pin_capture_blocks(c, r);
     *out = r;
     return B200_OK;
 }
@@ -272,6 +343,7 @@ int b200_graph_launch(b200_ctx* c, b200_graph* g) {
 int b200_graph_destroy(b200_graph* g) {
     if (g) {
         if (g->exec) cudaGraphExecDestroy(g->exec);
+        unpin_blocks(g);
         delete g;
     }
     return B200_OK;

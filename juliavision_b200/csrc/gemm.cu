@@ -570,13 +570,13 @@ static int64_t streamk_workers(int64_t tiles, int64_t workers_max) {
     return 0;
 }
 
-static TilePick pick_tile(int64_t M, int64_t N, int64_t K, int64_t nbatch, int sms) {
+static TilePick pick_tile(int64_t M, int64_t N, int64_t K, int64_t nbatch, int sms, bool allow_streamk = true) {
     if (const char* f = getenv("B200_GEMM_TILE")) { // debugging aid: "<bn>x<ncta>[s]", e.g. 256x2 or 256x2s
         int bn = 0, nc = 0;
         char sk = 0;
         const int got = sscanf(f, "%dx%d%c", &bn, &nc, &sk);
         if (got >= 2 && (bn == 256 || bn == 128 || (bn == 64 && nc == 1)) && (nc == 1 || nc == 2))
-            return {bn, nc, got == 3 && sk == 's'};
+            return {bn, nc, allow_streamk && got == 3 && sk == 's'};
     }
     struct Cand { int bn, ncta; double t_kb; };
     const Cand cands[5] = {{256, 2, 0.39}, {128, 2, 0.38}, {256, 1, 0.50}, {128, 1, 0.38}, {64, 1, 0.32}};
@@ -594,6 +594,7 @@ static TilePick pick_tile(int64_t M, int64_t N, int64_t K, int64_t nbatch, int s
         }
     }
     best_cost *= 0.85;
+    if (!allow_streamk) return best;
     for (const Cand& c : cands) {
         const int64_t tiles = cdiv(M, c.bn) * cdiv(N, (int64_t)GEMM_BM * c.ncta) * nbatch;
         const int64_t workers = sms / c.ncta;
@@ -777,7 +778,7 @@ namespace b200 {
 
 int gemm_f16_run(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
                  int64_t ldb, const void* bias, int bias_per_n, void* out, int64_t ldo, int out_dtype,
-                 int epilogue, int64_t nbatch, int64_t strideA, int64_t strideB, int64_t strideO) {
+                 int epilogue, int64_t nbatch, int64_t strideA, int64_t strideB, int64_t strideO, int use_workspace) {
     B200_REQUIRE(ctx, B200_EINVAL, "gemm: null ctx");
     B200_REQUIRE(M >= 0 && N >= 0 && K >= 0 && nbatch >= 0, B200_EINVAL, "gemm: negative extent");
     B200_REQUIRE(epilogue >= B200_EPI_NONE && epilogue <= B200_EPI_GELU_TANH, B200_EINVAL,
@@ -811,7 +812,7 @@ int gemm_f16_run(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, 
         B200_CUDA(cudaGetLastError());
         return B200_OK;
     }
-    const TilePick t = pick_tile(M, N, K, nbatch, ctx->prop.multiProcessorCount);
+    const TilePick t = pick_tile(M, N, K, nbatch, ctx->prop.multiProcessorCount, use_workspace != 0);
 #define GEMM_GO(BN_, T_, NC_)                                                                                     \
     return launch_tc<BN_, T_, NC_>(ctx, M, N, K, A, lda, B, ldb, bias, bias_per_n, out, ldo, epilogue, nbatch, strideA, \
                                    strideB, strideO, t.streamk)

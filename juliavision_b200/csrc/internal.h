@@ -8,6 +8,8 @@
 #include <map>
 #include <mutex>
 #include <unordered_map>
+#include <unordered_set>
+#include <utility>
 #include <vector>
 
 #include "../../include/b200dnn.h"
@@ -63,6 +65,14 @@ struct b200_ctx {
     void* ws_buf = nullptr;
     size_t ws_cap = 0, ws_used = 0;
     std::vector<b200::RetiredBlock> ws_retired;
+
+    // Blocks a recorded graph has baked into its launches (pool blocks handed out and workspace
+    // blocks used while capturing).  A pinned block that is freed waits in `held` instead of the
+    // free list, so no later allocation can receive memory a replay will still write.
+    std::vector<std::pair<void*, size_t>> capture_blocks;   // collected between graph_begin and graph_end
+    std::unordered_map<void*, int> pinned;                  // block -> number of live graphs that use it
+    std::unordered_map<void*, size_t> held;                 // freed while pinned: block -> size
+    std::unordered_set<b200_graph*> graphs;                 // live graphs recorded on this context
 };
 
 constexpr int SK_FLAG_COUNT = 4096;
@@ -70,6 +80,8 @@ constexpr int GEMV_COUNTER_COUNT = 4096;   // arrival counters of the split matr
 
 struct b200_graph {
     cudaGraphExec_t exec = nullptr;
+    b200_ctx* ctx = nullptr;      // null once the context is gone
+    std::vector<void*> pins;      // pool blocks this graph keeps out of circulation
 };
 
 namespace b200 {
@@ -91,10 +103,13 @@ int attention_window_launch(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
                             float scale);
 
 // GEMM with the bias broadcast along either axis (bias_per_n = 1: one value per column j,
-// which is what a convolution lowered to a GEMM over pixels needs).
+// which is what a convolution lowered to a GEMM over pixels needs).  use_workspace = 0 keeps the
+// planner to schedules that need no scratch memory (whole tiles only), so the call touches neither
+// the workspace nor the pool.
 int gemm_f16_run(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
                  int64_t ldb, const void* bias, int bias_per_n, void* out, int64_t ldo, int out_dtype,
-                 int epilogue, int64_t nbatch, int64_t strideA, int64_t strideB, int64_t strideO);
+                 int epilogue, int64_t nbatch, int64_t strideA, int64_t strideB, int64_t strideO,
+                 int use_workspace = 1);
 
 inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

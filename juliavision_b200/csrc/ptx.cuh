@@ -22,7 +22,8 @@ enum : int {
     KST_WAIT_TMEM_EMPTY = 104, // MMA issuer waited for an accumulator never drained
     KST_WAIT_SOFTMAX = 105,    // attention: a softmax <-> MMA hand-off never arrived
     KST_SMEM_LAYOUT = 106,     // dynamic shared memory base left no room for the carve-up
-    KST_WAIT_STREAMK = 107     // a stream-K finisher waited for a partial tile that never came
+    KST_WAIT_STREAMK = 107,    // a stream-K finisher waited for a partial tile that never came
+    KST_WAIT_SELFTEST = 108    // the self-test's wait on a barrier nothing arrives at ran out, as it must
 };
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // 2 s
@@ -95,7 +96,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  `abort_flag` is a CTA-shared word any role raises when it gives up, so the
 // other roles leave their own waits promptly instead of each running out its own clock.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* d_status, int code,
-                                          volatile int* abort_flag) {
+                                          volatile int* abort_flag,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = globaltimer_ns();
     uint32_t spins = 0;
@@ -103,7 +105,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* d
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 atomicCAS(d_status, 0, code);
                 *abort_flag = 1;
                 return false;

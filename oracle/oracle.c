@@ -54,6 +54,18 @@ int ora_num_threads(void) {
 #endif
 }
 
+/* Thread count of the parallel loops below, overriding an inherited OMP_NUM_THREADS (launchers
+ * that start one process per GPU export OMP_NUM_THREADS=1).  Returns the count now in force. */
+int ora_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 /* ------------------------------------------------------------------ activations */
 
 /* ops.jl:161-169 — Abramowitz & Stegun 7.1.26, evaluated in fp32 for half input. */

@@ -66,6 +66,18 @@ def num_threads() -> int:
     return lib().ora_num_threads()
 
 
+def set_num_threads(n: int) -> int:
+    """Use `n` threads from now on, whatever OMP_NUM_THREADS said at load time; returns the count in force."""
+    L = lib()
+    L.ora_set_num_threads.restype = C.c_int
+    return L.ora_set_num_threads(C.c_int(int(n)))
+
+
+def use_all_cores() -> int:
+    """Use every core this process may run on (its affinity mask)."""
+    return set_num_threads(len(os.sched_getaffinity(0)))
+
+
 def act(x: np.ndarray, name: str) -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=np.float16)
     y = np.empty_like(x)

@@ -83,6 +83,23 @@ def test_config3_shape_one_layer_vs_oracle(ctx):
     assert relerr(got, ref) < 1e-2, describe(got, ref, 1e-2)
 
 
+def test_config3_four_layer_prefix_at_full_geometry_vs_oracle(ctx):
+    """The benchmarked stack deeper than one layer at its real size: the residual stream after 4 of the
+    32 layers (d 1280, 20 heads of 64, FFN 5120, 1500 tokens) against the oracle's prefix — the
+    reference's own gate is a block prefix on its CPU backend (verify.jl:115-118) — and the closing
+    layer norm of a 4-layer stack on top of it."""
+    from oracle.encoder_ref import oracle_forward
+    full = EncoderConfig()
+    cfg = EncoderConfig(layers=4)
+    x = np.float16(np.random.default_rng(8).standard_normal((cfg.tokens, cfg.d_model)))
+    enc, w, got = _run(ctx, cfg, x, graph=True)
+    ref_prefix = oracle_forward(full, w, x, layers=4)            # no closing layer norm: 4 < 32
+    stream = enc.x.to_host()
+    assert relerr(stream, ref_prefix) < 1e-2, describe(stream, ref_prefix, 1e-2)
+    ref = oracle_forward(cfg, w, x)
+    assert relerr(got, ref) < 1e-2, describe(got, ref, 1e-2)
+
+
 def test_exported_graph_through_execute_equals_direct_calls(ctx):
     """The same encoder as an exported-graph JSON, run by Model/execute! with the static slab plan and
     the load-time rewrites, must give the op-by-op pass bit for bit — planned, with no allocation

@@ -4,6 +4,7 @@ import numpy as np
 import pytest
 
 import juliavision_b200 as jv
+from juliavision_b200 import _lib
 from juliavision_b200.graph import loadgraph
 
 from .conftest import relerr
@@ -118,3 +119,76 @@ def test_conv_bn_relu_graph_runs_as_one_convolution(ctx, ora):
     s = w["bn.weight"] / np.sqrt(w["bn.var"] + np.float32(1e-5))
     want = np.maximum(c * s[None, :, None, None] + (w["bn.bias"] - w["bn.mean"] * s)[None, :, None, None], 0)
     assert relerr(y.to_host(), want) < 2e-2
+
+
+def test_memory_a_graph_uses_is_not_handed_to_anyone_else(ctx):
+    """A recorded graph bakes in the addresses of the workspace block and of any pool block handed out
+    while capturing.  Growing the workspace afterwards retires the old block, and freeing a capture-time
+    temporary returns it; neither may reach a later allocation while the graph lives, or a replay would
+    scribble over someone else's array.  Split matrix-vector products are used because they leave
+    partial sums in the workspace on every call."""
+    import ctypes as C
+    with jv.Ctx(0) as c:
+        rng = np.random.default_rng(12)
+        M, K = 256, 4096
+        Wt = c.toback(np.float16(rng.standard_normal((K, M)) * 0.05))
+        xv = c.toback(np.float16(rng.standard_normal((1, K))))
+        out = c.allocate(np.float16, M, 1)
+        temps = []
+
+        def step():
+            c.ws.reset()
+            temps.append(c.allocate(np.float16, 1 << 18))     # a pool block taken while capturing
+            jv.matmul_(c, out, Wt, xv, None)
+
+        step()                       # warm: pool and workspace have what the capture will need
+        temps.clear()
+        c.synchronize()
+        g = c.capture(step)
+        ws_cap = c.ws.stats()[1]
+        temps.clear()                # the capture-time block is freed by its owner ...
+        c.ws.reset()
+        c.ws.scratch(np.uint8, 4 * ws_cap)   # ... and the workspace grows, retiring the block the graph uses
+        c.ws.reset()
+        # Everything allocated now must be disjoint from what the graph writes: fill a lot of memory of
+        # the same size classes with a pattern, replay, and look at the pattern again.
+        guards = [c.allocate(np.uint8, n) for n in (1 << 19, ws_cap, 1 << 19, ws_cap, 1 << 20)]
+        for a in guards:
+            c.fill_bytes(a, 0x5A)
+        c.fill_bytes(out, 0)
+        for _ in range(3):
+            g.replay()
+        c.synchronize()
+        want = (np.float32(xv.to_host()) @ np.float32(Wt.to_host())).ravel()
+        assert relerr(out.to_host().ravel(), want) < 1e-2
+        for a in guards:
+            assert np.all(a.to_host() == 0x5A), "a replay wrote into memory allocated after the capture"
+        del g                        # destroying the graph puts its blocks back into circulation
+        use, res = C.c_size_t(), C.c_size_t()
+        _lib.check(_lib.lib().b200_pool_stats(c.handle, C.byref(use), C.byref(res)))
+        again = c.allocate(np.uint8, ws_cap)
+        use2, res2 = C.c_size_t(), C.c_size_t()
+        _lib.check(_lib.lib().b200_pool_stats(c.handle, C.byref(use2), C.byref(res2)))
+        assert res2.value == res.value, "the released workspace block was not reused"
+
+
+def test_a_wait_that_cannot_be_satisfied_runs_out_and_the_context_carries_on(ctx):
+    """Bounded waits: a one-warp kernel waits 2 ms on a barrier nothing arrives at.  It must return, the
+    next sync must report the kernel status once, and the same context must then compute correctly."""
+    import ctypes as C
+    with jv.Ctx(0) as c:
+        flag = c.allocate(np.int32, 1)
+        c.fill_bytes(flag, 0)
+        _lib.check(_lib.lib().b200_selftest_bounded_wait(c.handle, 2_000_000, flag.ptr))
+        with pytest.raises(jv.B200Error) as e:
+            c.synchronize()
+        assert e.value.code == _lib.EKERNEL and "108" in str(e.value)
+        assert int(flag.to_host()[0]) == 1
+        c.synchronize()              # the status was cleared by the failing sync
+        rng = np.random.default_rng(13)
+        X = np.float16(rng.standard_normal((300, 256)) * 0.25)
+        Wt = np.float16(rng.standard_normal((256, 512)) * 0.25)
+        y = c.allocate(np.float16, 512, 300)
+        jv.matmul_(c, y, c.toback(Wt), c.toback(X), None)
+        c.synchronize()
+        assert relerr(y.to_host(), np.float32(X) @ np.float32(Wt)) < 1e-2

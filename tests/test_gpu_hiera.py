@@ -88,3 +88,24 @@ def test_hiera_full_size_properties(ctx):
     assert np.array_equal(a, b)
     assert np.array_equal(a[0], a[1])
     assert float(np.std(a.astype(np.float32))) > 1e-3
+
+
+def test_hiera_full_size_matches_raster_oracle(ctx):
+    """The benchmarked configuration itself — 1024x1024x3 image, all 24 blocks (8x8 and 16x16 windows,
+    three global blocks, three pooling blocks), 32x32x896 out — against the raster-order oracle on the
+    same seeded image and weights.  The oracle's pass is 0.62 TFLOP of scalar fp32 work: tens of seconds
+    on the host cores."""
+    from oracle import oracle as ora
+    from oracle.hiera_ref import oracle_forward
+    ora.use_all_cores()
+    cfg = HieraConfig()
+    w = init_weights(cfg)
+    img = np.float16(np.random.default_rng(6).random((1, cfg.in_ch, cfg.image, cfg.image)))
+    model = Hiera(ctx, cfg, w, batch=1)
+    ctx.upload(model.image, img)
+    got = model.forward().to_host()
+    ctx.synchronize()
+    ref = oracle_forward(cfg, w, img)
+    assert got.shape == ref.shape == (1, 32, 32, 896)
+    assert np.all(np.isfinite(got))
+    assert relerr(got, ref) < 1e-2, describe(got, ref, 1e-2)
