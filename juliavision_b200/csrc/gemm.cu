@@ -12,11 +12,13 @@
 // Replaces matmul_coopmat! + Lava.coopmat_gemm! + padcols_kernel! + mm_epilogue_kernel!
 // (reference kernels/extern/matmul.jl:172-273).
 //
-// Roles inside one persistent CTA (576 threads):
+// Roles inside one persistent CTA (608 threads):
 //   warp 0     TMA producer  (one lane)        global -> shared ring, STAGES deep
-//   warp 1     UMMA issuer   (one lane)        shared -> TMEM accumulators (two, ping-pong)
+//   warp 1     UMMA issuer   (one lane issues) shared -> TMEM accumulators (two, ping-pong)
 //   warps 2-17 epilogue      (512 threads)     TMEM -> registers -> +bias, round, act ->
 //                                              warp-private shared slab -> bulk tensor store
+//   warp 18    relay                           waits for each stage to land and passes that on to the
+//                                              issuer through a named barrier (see the issuer's comment)
 #include <cuda_fp16.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -30,7 +32,9 @@ namespace b200 {
 constexpr int GEMM_BM = 128; // tokens per CTA (TMEM lanes)
 constexpr int GEMM_BK = 64;  // one 128-byte swizzle row of fp16
 constexpr int EPI_WARPS = 16;
-constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS; // producer warp, UMMA warp, epilogue warps
+constexpr int RELAY_WARP = 2 + EPI_WARPS;
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS + 32; // producer warp, UMMA warp, epilogue warps, relay warp
+static_assert(GEMM_BK == 64, "the UMMA issuer unrolls four K = 16 steps per k-block");
 constexpr int SMEM_LIMIT = 232448; // 227 KB
 
 // NCTA = 1: one CTA per tile of 128 tokens x BN features (tcgen05.mma.cta_group::1).
@@ -251,56 +255,83 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         }
     } else if (warp == 1) {
         // -------------------------------------------------------------- UMMA issuer
-        if (lane == 0 && rank == 0) {
+        // What one k-block costs the issuing thread, measured with the SM's cycle counter on a stand-alone
+        // loop of the same instructions: 64 cycles per tcgen05.mma (whatever N), ~45 for the commit, and
+        // ~215 more for the first shared-memory read after them whose value the thread needs — which is what
+        // an mbarrier test is.  4 x 64 + 45 + 215 made every k-block take 560-590 cycles for every tile width,
+        // above the 512 the tensor pipe needs for a 256-wide pair tile.  So this thread never reads shared
+        // memory in its loop: the relay warp watches the stage barriers and hands each "stage has landed"
+        // over through a named barrier (a hardware barrier, ~100 cycles here), one per stage of the ring.
+        // The whole warp runs the loop so that the barrier instruction is warp-uniform; lane 0 issues.
+        if (rank == 0) {
             constexpr uint32_t idesc = make_idesc_f16(TILE_N, BN, /*a K-major*/ 0, /*b MN-major*/ 1);
             constexpr uint64_t adesc0 = make_smem_desc(16, 1024);
             constexpr uint64_t bdesc0 = make_smem_desc(Cfg::B_CHUNK_BYTES, 1024);
             int s = 0;
-            uint32_t ph = 0;
-            bool ok = true;
             int64_t it = 0;
             SegIter seg;
-            for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); ok && seg.valid(); seg.next(), ++it) {
+            for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); seg.valid(); seg.next(), ++it) {
                 const int acc = (int)(it & 1);
                 const uint32_t aph = (uint32_t)((it >> 1) & 1);
-                if constexpr (NCTA == 2) {
-                    if (!mbar_wait_cluster(&tempty[acc], aph ^ 1, p.d_status, KST_WAIT_TMEM_EMPTY, abort_flag)) break;
-                } else {
-                    if (!mbar_wait(&tempty[acc], aph ^ 1, p.d_status, KST_WAIT_TMEM_EMPTY, abort_flag)) break;
-                }
-                tc_fence_after();
+                bool got;
+                if constexpr (NCTA == 2) got = mbar_wait_cluster(&tempty[acc], aph ^ 1, p.d_status, KST_WAIT_TMEM_EMPTY, abort_flag);
+                else got = mbar_wait(&tempty[acc], aph ^ 1, p.d_status, KST_WAIT_TMEM_EMPTY, abort_flag);
+                if (__any_sync(0xffffffffu, !got)) break;   // one answer per warp; the relay keeps arriving, which is harmless
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
-                    bool got;
-                    if constexpr (NCTA == 2) got = mbar_wait_cluster(&full[s], ph, p.d_status, KST_WAIT_FULL, abort_flag);
-                    else got = mbar_wait(&full[s], ph, p.d_status, KST_WAIT_FULL, abort_flag);
-                    if (!got) {
-                        ok = false;
-                        break;
-                    }
+                    named_bar_sync(1 + s, 64);   // the relay has seen full[s] complete (or has given up: see there)
                     tc_fence_after();
-                    if (kb == seg.kb0 && it == 0) GEMM_TRACE(3); // first stage landed
-                    const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+                    if (lane == 0) {
+                        if (kb == seg.kb0 && it == 0) GEMM_TRACE(3); // first stage landed
+                        const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                        const uint32_t b_addr = a_addr + Cfg::A_BYTES;
 #pragma unroll
-                    for (int k = 0; k < GEMM_BK / 16; ++k) {
-                        // K-major A: +16 elements of K = +32 B inside the swizzle row.
-                        // MN-major B: +16 k-rows = two 8-row groups = +2048 B.
-                        const uint64_t ad = smem_desc_at(adesc0, a_addr + k * 32);
-                        const uint64_t bd = smem_desc_at(bdesc0, b_addr + k * 2048);
-                        const uint32_t accum = (kb != seg.kb0 || k != 0); // a segment starts a fresh accumulator
-                        if constexpr (NCTA == 2) umma_ss_pair(d_tmem, ad, bd, idesc, accum);
-                        else umma_ss(d_tmem, ad, bd, idesc, accum);
+                        for (int k = 0; k < GEMM_BK / 16; ++k) {
+                            // K-major A: +16 elements of K = +32 B inside the swizzle row.
+                            // MN-major B: +16 k-rows = two 8-row groups = +2048 B.
+                            const uint64_t ad = smem_desc_at(adesc0, a_addr + k * 32);
+                            const uint64_t bd = smem_desc_at(bdesc0, b_addr + k * 2048);
+                            const uint32_t accum = (kb != seg.kb0 || k != 0); // a segment starts a fresh accumulator
+                            if constexpr (NCTA == 2) umma_ss_pair(d_tmem, ad, bd, idesc, accum);
+                            else umma_ss(d_tmem, ad, bd, idesc, accum);
+                        }
+                        if constexpr (NCTA == 2) umma_commit_pair(&empty[s], 3); // frees the stage in both CTAs
+                        else umma_commit(&empty[s]);
                     }
-                    if constexpr (NCTA == 2) umma_commit_pair(&empty[s], 3); // frees the stage in both CTAs
-                    else umma_commit(&empty[s]);
-                    if (++s == Cfg::STAGES) { s = 0; ph ^= 1; }
+                    __syncwarp();
+                    if (++s == Cfg::STAGES) s = 0;
                 }
-                if (ok) {
+                if (lane == 0) {
                     if constexpr (NCTA == 2) umma_commit_pair(&tfull[acc], 3);
                     else umma_commit(&tfull[acc]);
+                    GEMM_TRACE(4 + (it < 4 ? it : 3)); // all UMMAs of tile `it` issued
                 }
-                GEMM_TRACE(4 + (it < 4 ? it : 3)); // all UMMAs of tile `it` issued
+                __syncwarp();
+            }
+        }
+    } else if (warp == RELAY_WARP) {
+        // -------------------------------------------------------------------- relay
+        // Waits (bounded) for each stage's operands to land and arrives on that stage's named barrier, on
+        // which the issuer warp syncs.  It can run ahead of the issuer by at most the ring depth, because
+        // stage s is refilled only after the issuer's commit for it, so one barrier id per stage suffices.
+        // After a wait has run out it stops waiting but keeps arriving, so the issuer is never left
+        // blocked: the UMMAs then run on whatever the stages hold, the status word says the result is void.
+        if (rank == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            SegIter seg;
+            for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); seg.valid(); seg.next()) {
+                for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
+                    if (ok) {
+                        bool got;
+                        if constexpr (NCTA == 2) got = mbar_wait_cluster(&full[s], ph, p.d_status, KST_WAIT_FULL, abort_flag);
+                        else got = mbar_wait(&full[s], ph, p.d_status, KST_WAIT_FULL, abort_flag);
+                        ok = !__any_sync(0xffffffffu, !got);
+                    }
+                    named_bar_arrive(1 + s, 64);
+                    if (++s == Cfg::STAGES) { s = 0; ph ^= 1; }
+                }
             }
         }
     } else {

@@ -211,6 +211,11 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Arrive without waiting: the producer side of a named barrier whose consumers bar.sync on it.
+__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 // Named barrier that also ORs a predicate across its participants: every thread gets the same
 // answer, so a "leave the loop" decision taken on it can never split the group.
 __device__ __forceinline__ bool named_bar_or(int id, int nthreads, bool pred) {
