@@ -79,6 +79,31 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Packed pairs of fp32 (sm_100): one instruction does two lanes' worth, which halves the softmax threads'
+// FMA and add streams; the exponentials themselves stay on the MUFU pipe.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ void tmem_st16_raw(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -249,6 +274,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                             idesc_s, k != 0);
                 umma_commit(&s_full[t]);
                 umma_commit(&k_empty[sk]);   // one of `ntiles` arrivals that free this K stage
+                if (j >= 1 && j < 7) ATT_TRACE(64 * t + 8 + 8 * (j - 1) + 0);   // Q K'(j) issued, filed under block j-1
                 return true;
             };
 
@@ -258,6 +284,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 if (j + 1 < nblk && !issue_qk(j + 1)) break;
                 const int sv = j % ATT_KV_STAGES;
                 if (!mbar_wait(&v_full[sv], (uint32_t)((j / ATT_KV_STAGES) & 1), p.d_status, KST_WAIT_FULL, abort_flag)) break;
+                if (j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 7);   // issuer reaches its wait for P(j)
                 if (!mbar_wait(&p_full[t], (uint32_t)(j & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag)) break;
                 tc_fence_after();
                 const uint32_t v_addr = smem_u32(tile_ptr(ATT_T_V + sv));
@@ -269,6 +296,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 }
                 umma_commit(&pv_done[t]);
                 umma_commit(&v_empty[sv]);   // one of `ntiles` arrivals that free this V stage
+                if (j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 1);   // P V(j) issued
             }
         }
     } else {
@@ -362,11 +390,11 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        mxa = fmaxf(mxa, __uint_as_float(r[c][i]));
-                        mxb = fmaxf(mxb, __uint_as_float(r[c][i + 1]));
-                        mxc = fmaxf(mxc, __uint_as_float(r[c][i + 2]));
-                        mxd = fmaxf(mxd, __uint_as_float(r[c][i + 3]));
+                    for (int i = 0; i < 32; i += 8) {   // three-input max: two scores per instruction
+                        mxa = fmax3(mxa, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+                        mxb = fmax3(mxb, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
+                        mxc = fmax3(mxc, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
+                        mxd = fmax3(mxd, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
                     }
                 }
                 const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
@@ -411,17 +439,20 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 if (lane == 0 && quad == 0 && j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 5);  // rescale done, my turn
                 // P = 2^(s*scale - m): fp32 exponentials, their fp32 row sum, and P rounded to fp16
                 // (two keys per 32-bit column) straight into tensor memory for the P V product.
-                float ls0 = 0.f, ls1 = 0.f;
+                const uint64_t sc2 = pack2(sce, sce), nm2 = pack2(-m_sub, -m_sub);
+                uint64_t lsa = pack2(0.f, 0.f), lsb = pack2(0.f, 0.f);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float x0 = fmaf(__uint_as_float(r[c][2 * i]), sce, -m_sub);
-                        const float x1 = fmaf(__uint_as_float(r[c][2 * i + 1]), sce, -m_sub);
+                        // two scores per FMA and per add (packed fp32 pairs), one ex2 each, one convert for the pair
+                        const uint64_t x2 = fma2(pack2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])), sc2, nm2);
+                        float x0, x1;
+                        unpack2(x2, x0, x1);
                         const float e0 = ex2(x0), e1 = ex2(x1);
-                        ls0 += e0;
-                        ls1 += e1;
+                        if (i & 1) lsb = add2(lsb, pack2(e0, e1));
+                        else lsa = add2(lsa, pack2(e0, e1));
                         const __half2 h2 = __floats2half2_rn(e0, e1);
                         pk[i] = *reinterpret_cast<const uint32_t*>(&h2);
                     }
@@ -434,6 +465,8 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                     }
                 }
                 tmem_wait_st();
+                float ls0, ls1;
+                unpack2(add2(lsa, lsb), ls0, ls1);
                 l_run = l_run * alpha + (ls0 + ls1);
                 m_run = m_new;
                 tc_fence_before();
