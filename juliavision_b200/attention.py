@@ -46,7 +46,7 @@ def sdpaplan(ctx: Ctx, q: DeviceArray, k: DeviceArray, v: DeviceArray, bias=None
     arr = lambda a: (C.c_int64 * 4)(*a.strides)
     rc = _lib.lib().b200_attention_f16_supported(E, Lq, Lk, H, B, arr(q), arr(k), arr(v), 0)
     if rc == _lib.OK and all(a.ptr % 16 == 0 for a in (q, k, v)):
-        return FlashTCPlan()
+        return FlashTCPlan(EP=64 if E <= 64 else 128)
     if any(a.strides[0] != 1 and a.shape[0] != 1 for a in (q, k, v)):
         return Decline("wrapped")  # E must be contiguous; densify first (attention.jl:734-759)
     if rc in (_lib.OK, 18, 21):

@@ -22,23 +22,35 @@
 
 namespace b200 {
 
-constexpr int ATT_BR = 128;  // queries per tile (TMEM lanes); a CTA owns two tiles
+constexpr int ATT_BR = 128;  // queries per tile (TMEM lanes)
 constexpr int ATT_BC = 128;  // keys per block
-constexpr int ATT_EP = 64;   // head dim padded to one 128-byte swizzle row
 constexpr int ATT_THREADS = 384;  // warps 0-3, 4-7: softmax of tile 0, 1; warp 8: TMA; warps 9, 10: UMMA; 11 idle
-constexpr int ATT_TILE_BYTES = 128 * 128; // every operand tile is 128 rows x 128 B
-constexpr int ATT_KV_STAGES = 4;
+constexpr int ATT_TILE_BYTES = 128 * 128; // one swizzle atom of an operand tile: 128 rows x 128 B (64 fp16 of E)
 #ifndef ATT_TURN_AT
 #define ATT_TURN_AT 2   // after which quarter (0..3) of its exponentials a tile passes the turn
 #endif
-// shared-memory map, in 16 KB tiles
-constexpr int ATT_T_Q = 0;                         // 2 tiles
-constexpr int ATT_T_K = 2;                         // ATT_KV_STAGES tiles
-constexpr int ATT_T_V = ATT_T_K + ATT_KV_STAGES;   // ATT_KV_STAGES tiles
-constexpr int ATT_T_END = ATT_T_V + ATT_KV_STAGES;
-constexpr int ATT_SMEM_BYTES = ATT_T_END * ATT_TILE_BYTES + 256;
+// Two shapes of CTA, chosen by the head dimension:
+//   EP = 64  (E <= 64):        two query tiles of 128 per CTA, K/V rings of 4 stages x 16 KB
+//   EP = 128 (64 < E <= 128):  one query tile of 128 per CTA; every operand tile is two swizzle atoms along E
+//                              (columns 0-63, 64-127, the second zero-filled past E by the tensor map), S = Q K'
+//                              runs over both, O has 128 columns; K/V rings of 3 stages x 32 KB
+// The reference's own fused tiling is E = 72 padded to 80 (flash.jl:1149-1157, flashepad kernelplans.jl).
+template <int EP> struct AttCfg {
+    static_assert(EP == 64 || EP == 128, "head dim is padded to one or two swizzle atoms");
+    static constexpr int ATOMS = EP / 64;              // 16 KB atoms per operand tile
+    static constexpr int NT = EP == 64 ? 2 : 1;        // query tiles per CTA
+    static constexpr int KV_STAGES = EP == 64 ? 4 : 3;
+    static constexpr int OP_BYTES = ATOMS * ATT_TILE_BYTES;   // one Q, K or V tile
+    // shared-memory map, in 16 KB atoms
+    static constexpr int T_Q = 0;                              // NT tiles
+    static constexpr int T_K = NT * ATOMS;                     // KV_STAGES tiles
+    static constexpr int T_V = T_K + KV_STAGES * ATOMS;        // KV_STAGES tiles
+    static constexpr int T_END = T_V + KV_STAGES * ATOMS;
+    static constexpr int SMEM_BYTES = T_END * ATT_TILE_BYTES + 256;
+    static_assert(SMEM_BYTES <= 232448, "shared memory over budget");
+};
 // tensor-memory map (512 columns): S of tile t, fp32, at [128 t, 128 t + 128); O of tile t, fp32, at
-// [256 + 64 t, ... + 64); P of tile t, fp16 packed two keys per column, at [384 + 64 t, ... + 64)
+// [256 + EP t, ... + EP); P of tile t, fp16 packed two keys per column, at [384 + 64 t, ... + 64)
 constexpr int ATT_TMEM_COLS = 512;
 constexpr int ATT_S_COL = 0;
 constexpr int ATT_O_COL = 256;
@@ -50,8 +62,8 @@ struct AttnParams {
     void* out;
     int64_t osL, osH, osB;  // element strides of out along L, H, B (E is contiguous)
     int out_f32;
-    int qpairs;         // query pairs (256 queries) per (head, batch)
-    int pair_ctas;      // CTAs [0, pair_ctas) own a whole pair; the rest own one tile of a pair each
+    int qpairs;         // work items per (head, batch): groups of NT query tiles ("pairs" when NT = 2)
+    int pair_ctas;      // CTAs [0, pair_ctas) own a whole item; the rest own one tile of a pair, or a key range of an item
     int* d_status;
     unsigned long long* trace;  // optional timeline of CTA (0,0,0) (globaltimer ns), null in normal use
     // Additive mask of the mem-efficient variant (attention.jl:55-59), (Lk,Lq,H,B) fp16 with element
@@ -124,11 +136,15 @@ __device__ __forceinline__ void tmem_st16_raw(uint32_t taddr, const uint32_t* r)
 // the P V product takes its A operand from there, so the shared-memory port only feeds K and V.
 // BIAS: the scaled score gets an additive fp16 mask before the softmax; a row whose keys are all
 // blocked (-inf everywhere) comes out as zeros, as in attn_softmax (attention.jl:73-100).
-template <bool BIAS>
+template <int EP, bool BIAS>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                         const __grid_constant__ CUtensorMap tmapK,
                         const __grid_constant__ CUtensorMap tmapV, const AttnParams p) {
+    using Cfg = AttCfg<EP>;
+    constexpr int ATT_KV_STAGES = Cfg::KV_STAGES;
+    constexpr int NT = Cfg::NT;
+    constexpr int ITEM_ROWS = NT * ATT_BR;   // queries one whole work item covers
     extern __shared__ __align__(1024) uint8_t smem[];
     // Uniform across the grid: a base that is not 1024-aligned makes every thread leave before
     // any barrier or TMEM allocation exists.
@@ -137,7 +153,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
         return;
     }
     auto tile_ptr = [&](int t) { return smem + t * ATT_TILE_BYTES; };
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_T_END * ATT_TILE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::T_END * ATT_TILE_BYTES);
     uint64_t* q_full = bars + 0;                           // [2]
     uint64_t* k_full = bars + 2;                           // [STAGES]
     uint64_t* k_empty = k_full + ATT_KV_STAGES;            // [STAGES]
@@ -175,11 +191,11 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
     const int qp = item % p.qpairs;
     const int h = (item / p.qpairs) % p.H;
     const int b = item / (p.qpairs * p.H);
-    const int q0 = qp * (2 * ATT_BR) + (half > 0 ? ATT_BR : 0);
+    const int q0 = qp * ITEM_ROWS + (half > 0 ? ATT_BR : 0);
     const int nblk_all = (p.Lk + ATT_BC - 1) / ATT_BC;
     const int jb0 = (int)((int64_t)split * nblk_all / nsp);           // first key block of this CTA
     const int nblk = (int)((int64_t)(split + 1) * nblk_all / nsp) - jb0;
-    const int ntiles = (half < 0 && q0 + ATT_BR < p.Lq) ? 2 : 1;   // the second tile may lie wholly past Lq
+    const int ntiles = (NT == 2 && half < 0 && q0 + ATT_BR < p.Lq) ? 2 : 1;   // the second tile may lie wholly past Lq
 
     if (threadIdx.x == 0) {
         ATT_TRACE(0);
@@ -225,18 +241,24 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (lane == 0) {
             for (int t = 0; t < ntiles; ++t) {
-                mbar_arrive_expect_tx(&q_full[t], ATT_TILE_BYTES);
-                tma_load_4d(tile_ptr(ATT_T_Q + t), &tmapQ, &q_full[t], 0, q0 + t * ATT_BR, h, b);
+                mbar_arrive_expect_tx(&q_full[t], Cfg::OP_BYTES);
+#pragma unroll
+                for (int a = 0; a < Cfg::ATOMS; ++a)
+                    tma_load_4d(tile_ptr(Cfg::T_Q + t * Cfg::ATOMS + a), &tmapQ, &q_full[t], a * 64, q0 + t * ATT_BR, h, b);
             }
             for (int j = 0; j < nblk; ++j) {
                 const int s = j % ATT_KV_STAGES;
                 const uint32_t ph = (uint32_t)((j / ATT_KV_STAGES) & 1);
                 if (!mbar_wait(&k_empty[s], ph ^ 1, p.d_status, KST_WAIT_EMPTY, abort_flag)) break;
-                mbar_arrive_expect_tx(&k_full[s], ATT_TILE_BYTES);
-                tma_load_4d(tile_ptr(ATT_T_K + s), &tmapK, &k_full[s], 0, (jb0 + j) * ATT_BC, h, b);
+                mbar_arrive_expect_tx(&k_full[s], Cfg::OP_BYTES);
+#pragma unroll
+                for (int a = 0; a < Cfg::ATOMS; ++a)
+                    tma_load_4d(tile_ptr(Cfg::T_K + s * Cfg::ATOMS + a), &tmapK, &k_full[s], a * 64, (jb0 + j) * ATT_BC, h, b);
                 if (!mbar_wait(&v_empty[s], ph ^ 1, p.d_status, KST_WAIT_EMPTY, abort_flag)) break;
-                mbar_arrive_expect_tx(&v_full[s], ATT_TILE_BYTES);
-                tma_load_4d(tile_ptr(ATT_T_V + s), &tmapV, &v_full[s], 0, (jb0 + j) * ATT_BC, h, b);
+                mbar_arrive_expect_tx(&v_full[s], Cfg::OP_BYTES);
+#pragma unroll
+                for (int a = 0; a < Cfg::ATOMS; ++a)
+                    tma_load_4d(tile_ptr(Cfg::T_V + s * Cfg::ATOMS + a), &tmapV, &v_full[s], a * 64, (jb0 + j) * ATT_BC, h, b);
             }
         }
     } else if (warp == 9 || warp == 10) {
@@ -252,12 +274,12 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
             // S = Q K': both operands K-major (E contiguous), from shared memory.  O += P V: P from
             // tensor memory, V MN-major (E contiguous per key) from shared memory.
             constexpr uint32_t idesc_s = make_idesc_f16(ATT_BR, ATT_BC, 0, 0);
-            constexpr uint32_t idesc_o = make_idesc_f16(ATT_BR, ATT_EP, 0, 1);
+            constexpr uint32_t idesc_o = make_idesc_f16(ATT_BR, EP, 0, 1);
             constexpr uint64_t kdesc0 = make_smem_desc(16, 1024);
             constexpr uint64_t vdesc0 = make_smem_desc(ATT_TILE_BYTES, 1024);
-            const uint32_t q_addr = smem_u32(tile_ptr(ATT_T_Q + t));
+            const uint32_t q_addr = smem_u32(tile_ptr(Cfg::T_Q + t * Cfg::ATOMS));
             const uint32_t s_tmem = tmem_base + ATT_S_COL + t * 128;
-            const uint32_t o_tmem = tmem_base + ATT_O_COL + t * 64;
+            const uint32_t o_tmem = tmem_base + ATT_O_COL + t * EP;
             const uint32_t p_tmem = tmem_base + ATT_P_COL + t * 64;
 
             auto issue_qk = [&](int j) -> bool {
@@ -267,11 +289,13 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 if (j > 0 && !mbar_wait(&s_empty[t], (uint32_t)((j - 1) & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag))
                     return false;
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(tile_ptr(ATT_T_K + sk));
+                const uint32_t k_addr = smem_u32(tile_ptr(Cfg::T_K + sk * Cfg::ATOMS));
 #pragma unroll
-                for (int k = 0; k < ATT_EP / 16; ++k)
-                    umma_ss(s_tmem, smem_desc_at(kdesc0, q_addr + k * 32), smem_desc_at(kdesc0, k_addr + k * 32),
-                            idesc_s, k != 0);
+                for (int k = 0; k < EP / 16; ++k) {
+                    // 16 elements of E = 32 B inside the swizzle row; every fourth step moves to the next atom
+                    const uint32_t off = (uint32_t)(k >> 2) * ATT_TILE_BYTES + (uint32_t)(k & 3) * 32;
+                    umma_ss(s_tmem, smem_desc_at(kdesc0, q_addr + off), smem_desc_at(kdesc0, k_addr + off), idesc_s, k != 0);
+                }
                 umma_commit(&s_full[t]);
                 umma_commit(&k_empty[sk]);   // one of `ntiles` arrivals that free this K stage
                 if (j >= 1 && j < 7) ATT_TRACE(64 * t + 8 + 8 * (j - 1) + 0);   // Q K'(j) issued, filed under block j-1
@@ -287,7 +311,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 if (j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 7);   // issuer reaches its wait for P(j)
                 if (!mbar_wait(&p_full[t], (uint32_t)(j & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag)) break;
                 tc_fence_after();
-                const uint32_t v_addr = smem_u32(tile_ptr(ATT_T_V + sv));
+                const uint32_t v_addr = smem_u32(tile_ptr(Cfg::T_V + sv * Cfg::ATOMS));
 #pragma unroll
                 for (int k = 0; k < ATT_BC / 16; ++k) {
                     // P comes from tensor memory: 16 keys = 8 packed columns per step.
@@ -308,7 +332,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
         if (t < ntiles) {
             const uint32_t lane_base = uint32_t(quad * 32) << 16;
             const uint32_t s_tmem = tmem_base + lane_base + ATT_S_COL + t * 128;
-            const uint32_t o_tmem = tmem_base + lane_base + ATT_O_COL + t * 64;
+            const uint32_t o_tmem = tmem_base + lane_base + ATT_O_COL + t * EP;
             const uint32_t p_tmem = tmem_base + lane_base + ATT_P_COL + t * 64;
             const float sc = p.scale_log2;
             const float sce = BIAS ? 1.0f : sc;   // with a bias the scores are rescaled when it is added
@@ -420,7 +444,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 // skipped warp-wide when no row's did — exact, the factor would be 1.
                 if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
-                    for (int c = 0; c < ATT_EP / 16; ++c) {   // 16 columns at a time: S is live in registers
+                    for (int c = 0; c < EP / 16; ++c) {   // 16 columns at a time: S is live in registers
                         uint32_t o16[16];
                         tmem_ld16(o_tmem + c * 16, o16);
                         tmem_wait_ld();
@@ -486,10 +510,10 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                     // Unnormalised rows and their (reference point, sum) for the merge.  tcgen05.ld is a
                     // warp-wide (.sync.aligned) instruction: every lane executes it, whether or not its
                     // row exists; only the stores are predicated.
-                    const int64_t prow = ((int64_t)split * p.ntail + tailpair) * (2 * ATT_BR) + t * ATT_BR + row;
+                    const int64_t prow = ((int64_t)split * p.ntail + tailpair) * ITEM_ROWS + t * ATT_BR + row;
                     float* po = p.part_o + prow * p.E;
 #pragma unroll 1
-                    for (int c = 0; c < ATT_EP / 32; ++c) {
+                    for (int c = 0; c < EP / 32; ++c) {
                         uint32_t r[32];
                         tmem_ld32(o_tmem + c * 32, r);
                         tmem_wait_ld();
@@ -510,7 +534,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 const float inv = 1.0f / (l_run == 0.f ? 1.0f : l_run);
                 const int64_t obase = lq * p.osL + h * p.osH + b * p.osB;
 #pragma unroll 1
-                for (int c = 0; c < ATT_EP / 32; ++c) {
+                for (int c = 0; c < EP / 32; ++c) {
                     uint32_t r[32];
                     tmem_ld32(o_tmem + c * 32, r);
                     tmem_wait_ld();
@@ -561,42 +585,40 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
 // query row; out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M the largest reference point.
 __global__ void __launch_bounds__(128)
 attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nsplit, int ntail,
-                       int first_pair, int qpairs, int E, int Lq, int H, void* out, int64_t osL, int64_t osH, int64_t osB,
-                       int out_f32) {
+                       int first_pair, int qpairs, int item_rows, int E, int Lq, int H, void* out, int64_t osL, int64_t osH,
+                       int64_t osB, int out_f32) {
     grid_dep_wait();
     const int lane = threadIdx.x & 31;
-    const int64_t rows = (int64_t)ntail * (2 * ATT_BR);
+    const int64_t rows = (int64_t)ntail * item_rows;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
-    const int pair = first_pair + (int)(row / (2 * ATT_BR));
-    const int lq = (pair % qpairs) * (2 * ATT_BR) + (int)(row % (2 * ATT_BR));
+    const int pair = first_pair + (int)(row / item_rows);
+    const int lq = (pair % qpairs) * item_rows + (int)(row % item_rows);
     if (lq >= Lq) return;
     const int h = (pair / qpairs) % H, b = pair / (qpairs * H);
     float M = -INFINITY;
     for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(s * rows + row) * 2]);
-    float den = 0.f, num0 = 0.f, num1 = 0.f;
+    float den = 0.f, num[4] = {0.f, 0.f, 0.f, 0.f};   // E <= 128: up to four elements per lane
     for (int s = 0; s < nsplit; ++s) {
         const float m = part_ml[(s * rows + row) * 2], l = part_ml[(s * rows + row) * 2 + 1];
         const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
         den = fmaf(l, w, den);
         const float* po = part_o + (s * rows + row) * E;
-        if (lane < E) num0 = fmaf(po[lane], w, num0);
-        if (lane + 32 < E) num1 = fmaf(po[lane + 32], w, num1);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (lane + 32 * u < E) num[u] = fmaf(po[lane + 32 * u], w, num[u]);
     }
     const float inv = 1.0f / (den == 0.f ? 1.0f : den);
     const int64_t obase = lq * osL + h * osH + b * osB;
-    if (out_f32) {
-        float* o = static_cast<float*>(out) + obase;
-        if (lane < E) o[lane] = num0 * inv;
-        if (lane + 32 < E) o[lane + 32] = num1 * inv;
-    } else {
-        __half* o = static_cast<__half*>(out) + obase;
-        if (lane < E) o[lane] = __float2half_rn(num0 * inv);
-        if (lane + 32 < E) o[lane + 32] = __float2half_rn(num1 * inv);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        if (lane + 32 * u >= E) continue;
+        if (out_f32) static_cast<float*>(out)[obase + lane + 32 * u] = num[u] * inv;
+        else static_cast<__half*>(out)[obase + lane + 32 * u] = __float2half_rn(num[u] * inv);
     }
 }
 
-// Scalar path for operands a tensor map cannot express (E > 64, E not a multiple of 8,
+// Scalar path for operands a tensor map cannot express (E > 128, E not a multiple of 8,
 // unaligned strides): one warp per query row, two passes over the keys.
 __global__ void attention_f16_scalar_kernel(int E, int Lq, int Lk, int H, int B, const __half* q, int64_t qsE, int64_t qsL, int64_t qsH, int64_t qsB,
                                             const __half* k, int64_t ksE, int64_t ksL, int64_t ksH, int64_t ksB,
@@ -658,7 +680,7 @@ __global__ void attention_f16_scalar_kernel(int E, int Lq, int Lk, int H, int B,
 static int tc_reason(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B, const int64_t* qs,
                      const int64_t* ks, const int64_t* vs) {
     if (E < 1 || Lq < 1 || Lk < 1 || H < 1 || B < 1) return B200_DECLINE_EXTENT;
-    if (E > ATT_EP || E % 8 != 0) return B200_DECLINE_TILING;
+    if (E > 128 || E % 8 != 0) return B200_DECLINE_TILING;
     if (H > 65535 || B > 65535 || Lq >= (1ll << 31) || Lk >= (1ll << 31)) return B200_DECLINE_EXTENT;
     const int64_t* ss[3] = {qs, ks, vs};
     for (int i = 0; i < 3; ++i) {
@@ -684,7 +706,7 @@ static int make_qkv_map(b200_ctx* ctx, CUtensorMap* m, const b200_strided4* t, i
     uint64_t s2 = st(2, s1 * (uint64_t)L);
     uint64_t s3 = st(3, s2 * (uint64_t)H);
     uint64_t str[3] = {s1, s2, s3};
-    uint32_t box[4] = {ATT_EP, 128, 1, 1};
+    uint32_t box[4] = {64, 128, 1, 1};   // one swizzle atom; a head dim above 64 takes two boxes per tile
     return make_tmap(ctx, m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, t->ptr, dims, str, box,
                      CU_TENSOR_MAP_SWIZZLE_128B);
 }
@@ -766,15 +788,19 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
     }
     static bool attr_done[16] = {};
     if (!attr_done[ctx->device & 15]) {
-        B200_CUDA(cudaFuncSetAttribute(attention_f16_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       ATT_SMEM_BYTES));
-        B200_CUDA(cudaFuncSetAttribute(attention_f16_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       ATT_SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(attention_f16_tc_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       AttCfg<64>::SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(attention_f16_tc_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       AttCfg<64>::SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(attention_f16_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       AttCfg<128>::SMEM_BYTES));
+        B200_CUDA(cudaFuncSetAttribute(attention_f16_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       AttCfg<128>::SMEM_BYTES));
         attr_done[ctx->device & 15] = true;
     }
     // Many windows of at most 64 keys: bound by HBM and latency, not by the tensor pipe; the small-tile
     // kernel keeps six CTAs per SM in flight where this one's set-up would cost more than the arithmetic.
-    if (bptr == nullptr && Lk <= 64 && B * H * cdiv(Lq, 64) > 2 * ctx->prop.multiProcessorCount)
+    if (bptr == nullptr && E <= 64 && Lk <= 64 && B * H * cdiv(Lq, 64) > 2 * ctx->prop.multiProcessorCount)
         return attention_window_launch(ctx, E, Lq, Lk, H, B, q, k, v, o, out_dtype, scale);
     CUtensorMap tq, tk, tv;
     int rc;
@@ -792,8 +818,18 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
     p.bias = bptr;
     p.bsK = bs[0]; p.bsQ = bs[1]; p.bsH = bs[2]; p.bsB = bs[3];
     p.bias_vec = bptr && bs[0] == 1 && al16(bptr) && bs[1] % 8 == 0 && bs[2] % 8 == 0 && bs[3] % 8 == 0;
-    p.qpairs = (int)cdiv(Lq, 2 * ATT_BR);
-    const int64_t pairs = (int64_t)p.qpairs * H * B;
+    const bool wide = E > 64;                              // two swizzle atoms along E, one query tile per CTA
+    const int64_t item_rows = wide ? AttCfg<128>::NT * ATT_BR : AttCfg<64>::NT * ATT_BR;
+    const size_t smem_bytes = wide ? AttCfg<128>::SMEM_BYTES : AttCfg<64>::SMEM_BYTES;
+    auto launch = [&](dim3 grid) -> cudaError_t {
+        if (wide)
+            return bptr ? launch_dep(attention_f16_tc_kernel<128, true>, grid, dim3(ATT_THREADS, 1, 1), smem_bytes, ctx->stream, 1, tq, tk, tv, p)
+                        : launch_dep(attention_f16_tc_kernel<128, false>, grid, dim3(ATT_THREADS, 1, 1), smem_bytes, ctx->stream, 1, tq, tk, tv, p);
+        return bptr ? launch_dep(attention_f16_tc_kernel<64, true>, grid, dim3(ATT_THREADS, 1, 1), smem_bytes, ctx->stream, 1, tq, tk, tv, p)
+                    : launch_dep(attention_f16_tc_kernel<64, false>, grid, dim3(ATT_THREADS, 1, 1), smem_bytes, ctx->stream, 1, tq, tk, tv, p);
+    };
+    p.qpairs = (int)cdiv(Lq, item_rows);
+    const int64_t pairs = (int64_t)p.qpairs * H * B;      // work items: pairs of query tiles, or single tiles when wide
     B200_REQUIRE(pairs < (1ll << 30), B200_DECLINE_EXTENT, "attention: too many query tiles");
     const int64_t sms = ctx->prop.multiProcessorCount;
     // Two cases cut pairs along the keys (at least two key blocks per piece) and merge afterwards:
@@ -817,7 +853,7 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
         if (ns > nblk_all / 2) ns = nblk_all / 2;
         if (ns > 64) ns = 64;
         if (ntail > 0 && ns >= 2) {
-            const int64_t rows = ntail * 2 * ATT_BR;
+            const int64_t rows = ntail * item_rows;
             void* ws = nullptr;
             rc = ws_scratch(ctx, (size_t)(ns * rows * (E + 2)) * sizeof(float), &ws);
             if (rc) return rc;
@@ -830,26 +866,19 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
     if (p.nsplit > 1) {
         p.pair_ctas = (int)(pairs - p.ntail);
         const int64_t ctas = p.pair_ctas + (int64_t)p.ntail * p.nsplit;
-        B200_CUDA(launch_dep(attention_f16_tc_kernel<false>, dim3((unsigned)ctas, 1, 1), dim3(ATT_THREADS, 1, 1),
-                             ATT_SMEM_BYTES, ctx->stream, 1, tq, tk, tv, p));
-        const int64_t rows = (int64_t)p.ntail * 2 * ATT_BR;
+        B200_CUDA(launch(dim3((unsigned)ctas, 1, 1)));
+        const int64_t rows = (int64_t)p.ntail * item_rows;
         B200_CUDA(launch_dep(attention_merge_kernel, dim3((unsigned)cdiv(rows, 4), 1, 1), dim3(128, 1, 1), 0, ctx->stream, 1,
-                             (const float*)p.part_o, (const float*)p.part_ml, p.nsplit, p.ntail, p.pair_ctas, p.qpairs, (int)E,
+                             (const float*)p.part_o, (const float*)p.part_ml, p.nsplit, p.ntail, p.pair_ctas, p.qpairs, (int)item_rows, (int)E,
                              (int)Lq, (int)H, out, o->stride[1], o->stride[2], o->stride[3], (int)(out_dtype == B200_F32)));
         ctx->launches += 2;
         return B200_OK;
     }
     // Split the pairs of a last wave that would leave more than half of the SMs idle — but not a
     // pair whose second tile does not exist.
-    int64_t nsplit = (pairs > sms && rem > 0 && 2 * rem <= sms && Lq % (2 * ATT_BR) == 0) ? rem : 0;
+    int64_t nsplit = (!wide && pairs > sms && rem > 0 && 2 * rem <= sms && Lq % (2 * ATT_BR) == 0) ? rem : 0;
     p.pair_ctas = (int)(pairs - nsplit);
-    dim3 grid((unsigned)(pairs + nsplit), 1, 1);
-    if (bptr)
-        B200_CUDA(launch_dep(attention_f16_tc_kernel<true>, grid, dim3(ATT_THREADS, 1, 1), ATT_SMEM_BYTES, ctx->stream, 1,
-                             tq, tk, tv, p));
-    else
-        B200_CUDA(launch_dep(attention_f16_tc_kernel<false>, grid, dim3(ATT_THREADS, 1, 1), ATT_SMEM_BYTES, ctx->stream, 1,
-                             tq, tk, tv, p));
+    B200_CUDA(launch(dim3((unsigned)(pairs + nsplit), 1, 1)));
     ctx->launches++;
     return B200_OK;
 }

@@ -45,7 +45,9 @@ class MMGemvPlan:
 @dataclass(frozen=True)
 class FlashTCPlan:
     """Fused single-pass attention on tcgen05; stands where FlashCMPlan stood
-    (kernelplans.jl:54-324). BR/BC are the query/key block, EP the padded head dim.  Holding this
+    (kernelplans.jl:54-324). BR/BC are the query/key block, EP the padded head dim (64 for E <= 64: two
+    query tiles per CTA; 128 for 64 < E <= 128, which covers the reference's own E = 72: one tile per
+    CTA, every operand two swizzle atoms along E).  Holding this
     plan means the call runs; inside it the library still chooses how: whole query-tile pairs, a key
     split with a merge for few queries over many keys, and for many windows of at most 64 keys a
     small-tile kernel (64 queries of one window and head per CTA) instead of the 128-row tiles."""

@@ -57,5 +57,6 @@ def test_supported_predicates_need_no_gpu():
                                           dense(64, 4096, 12), 0) == 0
     # an additive mask does not decline: the fused kernel takes it (b200_attention_f16_bias)
     assert L.b200_attention_f16_supported(64, 8, 8, 1, 1, dense(64, 8, 1), dense(64, 8, 1), dense(64, 8, 1), 1) == 0
-    assert _lib.DECLINE[L.b200_attention_f16_supported(72, 8, 8, 1, 1, dense(72, 8, 1), dense(72, 8, 1),
-                                                       dense(72, 8, 1), 0)] == "tiling"
+    assert L.b200_attention_f16_supported(72, 8, 8, 1, 1, dense(72, 8, 1), dense(72, 8, 1), dense(72, 8, 1), 0) == 0
+    assert _lib.DECLINE[L.b200_attention_f16_supported(136, 8, 8, 1, 1, dense(136, 8, 1), dense(136, 8, 1),
+                                                       dense(136, 8, 1), 0)] == "tiling"

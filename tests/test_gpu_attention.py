@@ -76,12 +76,52 @@ def test_token_major_output_view(ctx, ora):
     assert np.array_equal(got, dense)
 
 
-def test_head_dim_beyond_one_swizzle_row_takes_the_scalar_kernel(ctx, ora):
+# (E, Lq, Lk, H, B): the reference's own fused tiling and its tests are at head dim 72 (test_flash.jl:36,
+# 189-190, 221; FLASHCM_TILINGS flash.jl:1149-1157), SAM 2's windowed shape is (72,256,256,8,16)
+# (tools/attn_lab.jl:11-14); 80/96/104/128 cover the rest of the two-atom range
+WIDE = [(72, 64, 64, 1, 1), (72, 128, 128, 2, 1), (72, 256, 256, 2, 1), (72, 128, 256, 2, 2), (72, 64, 4096, 2, 1),
+        (72, 256, 256, 8, 16), (72, 1000, 700, 3, 2), (80, 300, 300, 2, 1), (96, 257, 129, 1, 2), (104, 130, 513, 2, 1),
+        (128, 384, 384, 2, 1), (128, 23, 4096, 4, 1)]
+
+
+@pytest.mark.parametrize("E,Lq,Lk,H,B", WIDE)
+def test_head_dims_above_one_swizzle_row_run_on_the_tensor_cores(ctx, ora, E, Lq, Lk, H, B):
+    """Head dims 72..128: two swizzle atoms along E, one query tile per CTA; same contract and tolerance
+    as the narrow kernel, ragged query/key tails and the few-queries key split included."""
+    rng = np.random.default_rng(E * 7 + Lq + Lk)
+    q = np.float16(rng.standard_normal((B, H, Lq, E)) * 0.2)
+    k = np.float16(rng.standard_normal((B, H, Lk, E)) * 0.2)
+    v = np.float16(rng.standard_normal((B, H, Lk, E)) * 0.2)
+    scale = 1 / np.sqrt(E)
+    for out_dtype in (np.float32, np.float16):
+        got, plan = attention_gpu(ctx, q, k, v, scale, out_dtype)
+        assert isinstance(plan, jv.FlashTCPlan), plan
+        assert np.all(np.isfinite(got))
+        ref = ora.attention_ref(q, k, v, scale)
+        assert np.max(np.abs(got)) > 1e-3
+        assert relerr(got, ref) < TOL, describe(got, ref, TOL)
+
+
+def test_sam2_global_shape_head_dim_72_sampled_rows(ctx, ora):
+    """(E72, L4096, H8, B1), the global-attention shape of the reference's flagship encoder
+    (tools/attn_lab.jl:11-14), checked on sampled query rows against the fp32 reference."""
+    rng = np.random.default_rng(72)
+    B, H, L, E = 1, 8, 4096, 72
+    q, k, v = (np.float16(rng.standard_normal((B, H, L, E)) * 0.5) for _ in range(3))
+    scale = 1 / np.sqrt(E)
+    got, plan = attention_gpu(ctx, q, k, v, scale)
+    assert isinstance(plan, jv.FlashTCPlan)
+    rows = np.unique(np.concatenate([np.arange(0, L, 97), [127, 128, 255, 256, L - 1]]))
+    ref = ora.attention_ref(q[:, :, rows], k, v, scale)
+    assert relerr(got[:, :, rows], ref) < TOL, describe(got[:, :, rows], ref, TOL)
+
+
+def test_head_dim_beyond_two_swizzle_rows_takes_the_scalar_kernel(ctx, ora):
     rng = np.random.default_rng(12)
-    q, k, v = (np.float16(rng.standard_normal((1, 2, 64, 72)) * 0.2) for _ in range(3))  # test_flash.jl:36
-    got, plan = attention_gpu(ctx, q, k, v, 1 / np.sqrt(72), np.float32)
+    q, k, v = (np.float16(rng.standard_normal((1, 2, 64, 136)) * 0.2) for _ in range(3))
+    got, plan = attention_gpu(ctx, q, k, v, 1 / np.sqrt(136), np.float32)
     assert isinstance(plan, jv.AttnScalarPlan)
-    assert relerr(got, ora.attention_ref(q, k, v, 1 / np.sqrt(72))) < TOL
+    assert relerr(got, ora.attention_ref(q, k, v, 1 / np.sqrt(136))) < TOL
 
 
 # torch (B,H,Lq,Lk,E) and the bias shape as torch (B|1, H|1, Lq|1, Lk|1)
@@ -89,7 +129,9 @@ BIAS_CASES = [((2, 3, 256, 384, 64), (2, 3, 256, 384)),    # full mask, rows rea
               ((2, 3, 300, 200, 56), (2, 3, 300, 200)),    # ragged keys: the guarded scalar reads
               ((2, 4, 256, 256, 64), (2, 1, 1, 256)),      # key-padding mask broadcast over heads and queries
               ((1, 2, 130, 257, 32), (1, 1, 130, 257)),    # broadcast over heads, odd row stride
-              ((1, 2, 64, 64, 72), (1, 2, 64, 64))]        # head dim past one swizzle row: scalar kernel
+              ((1, 2, 64, 64, 72), (1, 2, 64, 64)),        # head dim past one swizzle row: two atoms along E
+              ((2, 2, 300, 260, 96), (2, 1, 300, 260)),
+              ((1, 1, 40, 40, 136), (1, 1, 40, 40))]       # past two: scalar kernel
 
 
 @pytest.mark.parametrize("shape,bshape", BIAS_CASES)
@@ -109,7 +151,7 @@ def test_additive_bias_vs_oracle(ctx, ora, shape, bshape):
     scale = 1 / np.sqrt(E)
     for out_dtype in (np.float16, np.float32):
         got, plan = attention_gpu(ctx, q, k, v, scale, out_dtype, bias=bias)
-        assert isinstance(plan, jv.FlashTCPlan if E <= 64 else jv.AttnScalarPlan), plan
+        assert isinstance(plan, jv.FlashTCPlan if E <= 128 else jv.AttnScalarPlan), plan
         assert np.all(np.isfinite(got))
         ref = ora.attention_ref(q, k, v, scale, bias=bias)
         assert relerr(got, ref) < TOL, describe(got, ref, TOL)
