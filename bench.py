@@ -355,6 +355,95 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def config5_sweeps(ctx, jv, world: int, rank: int, dist, torch, local: int, quick: bool):
+    """BASELINE config 5 on `world` GPUs, timed on every rank (max over ranks), independent shards, no collective:
+    (1) the GEMM sweep M in {256..65536} x N in {1000, 3072, 5120} x K in {768, 1280} split along M (the token rows;
+    rank r computes the rows b200_shard_range gives it, W and b replicated); (2) 64 images through the Hiera-B+-shaped
+    encoder, 64/world per rank, 8 per pass."""
+    from juliavision_b200.hiera import Hiera, HieraConfig
+    from juliavision_b200.shard import shard_range
+    rng = np.random.default_rng(5 + rank)
+    Ms = [256 << i for i in range(9)]
+    Ns, Ks = (1000, 3072, 5120), (768, 1280)
+    reps = 5 if quick else 10
+    blockX = {K: np.float16(rng.standard_normal((4096, K), dtype=np.float32) * 0.05) for K in Ks}
+    gemm_ms = []
+    for K in Ks:
+        b0, e0 = shard_range(Ms[-1], world, rank, 256)
+        rows_max = max(e0 - b0, 256)
+        X = ctx.toback(np.tile(blockX[K], ((rows_max + 4095) // 4096, 1))[:rows_max])
+        for N in Ns:
+            Wt = ctx.toback(np.float16(rng.standard_normal((K, N), dtype=np.float32) * 0.05))
+            bias = ctx.toback(np.float16(rng.standard_normal(N, dtype=np.float32) * 0.05))
+            out = ctx.allocate(np.float16, N, rows_max)
+            for M in Ms:
+                lo, hi = shard_range(M, world, rank, 256)
+                rows = hi - lo
+                ms = 0.0
+                if rows > 0:
+                    Xv = jv.DeviceArray(ctx, X.ptr, np.float16, (K, rows), owner=X)
+                    Ov = jv.DeviceArray(ctx, out.ptr, np.float16, (N, rows), owner=out)
+                    def go():          # `reps` launches recorded once and replayed, so that the host's call rate
+                        for _ in range(reps):      # (~15 us per call from Python) is not what the small shapes show
+                            ctx.ws.reset()
+                            jv.matmul_(ctx, Ov, Wt, Xv, bias)
+                    go()
+                    ctx.synchronize()
+                    g = ctx.capture(go)
+                    g.replay()
+                    ctx.synchronize()
+                    ms = time_region(ctx, g.replay, 2) / reps
+                    del g
+                gemm_ms.append(ms)
+            del Wt, bias, out
+        del X
+    t = torch.tensor(gemm_ms, device=f"cuda:{local}", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    gemm_ms = [float(v) for v in t]
+    rows_out, i, tot_flop, tot_ms = [], 0, 0.0, 0.0
+    for K in Ks:
+        for N in Ns:
+            for M in Ms:
+                ms = gemm_ms[i]
+                i += 1
+                fl = 2.0 * M * N * K
+                tot_flop += fl
+                tot_ms += ms
+                rows_out.append(dict(M=M, N=N, K=K, ms=round(ms, 5), tflops=round(fl / ms / 1e9, 1) if ms > 0 else None))
+    gemm = dict(split="rows of X and Y along M over the ranks in 256-row units, W and b replicated; time = max over ranks",
+                launches_timed_per_shape=reps, total_ms=round(tot_ms, 4), aggregate_tflops=round(tot_flop / tot_ms / 1e9, 1),
+                shapes=rows_out)
+
+    cfg = HieraConfig()
+    images, per_pass = 64, 8
+    mine = images // world
+    passes = max(1, mine // per_pass)
+    model = Hiera(ctx, cfg, batch=min(per_pass, mine))
+    ctx.upload(model.image, np.float16(np.random.default_rng(21 + rank).random(
+        (model.batch, cfg.in_ch, cfg.image, cfg.image), dtype=np.float32)))
+    graph = model.capture()
+    for _ in range(2):
+        graph.replay()
+    ctx.synchronize()
+    steps = 2 if quick else 4
+    if dist is not None:
+        dist.barrier()
+    ctx.timer_start()
+    for _ in range(steps * passes):
+        graph.replay()
+    ms_step = ctx.timer_stop() / steps
+    t = torch.tensor([ms_step], device=f"cuda:{local}", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t[0])
+    hiera = dict(images=images, images_per_gpu=mine, images_per_pass=model.batch, passes_per_step=passes, steps=steps,
+                 ms_per_step=round(ms_step, 4), ms_per_img=round(ms_step / images, 4),
+                 tflops_per_gpu=round(cfg.flops(mine) / ms_step / 1e9, 1))
+    del model, graph
+    return dict(gemm_split_along_M=gemm, hiera_64_images=hiera)
+
+
 def run_hiera(args):
     """The image workload of the scaling sweep: `--images` 1024x1024 images per GPU (64 images over 8 GPUs =
     8 each) through the Hiera-B+-shaped encoder, one pass per step replayed as a CUDA graph; images are
@@ -418,10 +507,49 @@ def run_hiera(args):
     e2e_ms = ctx.timer_stop() / args.steps
     barrier()
     clocks = sampler.stop()
+    # dominant kernel family of the pass alone: its GEMM launches replayed back to back on the pass's buffers
+    model.gemm_pass()
+    ctx.synchronize()
+    ggraph = ctx.capture(model.gemm_pass)
+    for _ in range(2):
+        ggraph.replay()
+    ctx.synchronize()
+    n0 = ctx.launch_count()
+    model.gemm_pass()
+    n_gemm = ctx.launch_count() - n0
+    gemm_ms = time_region(ctx, ggraph.replay, max(3, args.steps // 2))
+    pk = peaks()
+    gemm_tflops = model.gemm_flops() / gemm_ms / 1e9
+    roofline = dict(bound="tensor", kernel="gemm_f16_tc_kernel", achieved=round(gemm_tflops, 1), peak=pk["tflops"],
+                    unit="TFLOP/s", frac=round(gemm_tflops / pk["tflops"], 4),
+                    peak_source=f"{pk['source']} (bf16 burst); spec dense fp16 2250", launches=n_gemm,
+                    avg_launch_ms=round(gemm_ms / n_gemm, 5), traffic=None,
+                    note="all projection/MLP GEMM launches of one pass replayed back to back; 2MNK unpadded; the K = 112 "
+                         "and 224 GEMMs of the first two stages are bound by their output stream, not by the tensor pipe")
     if dist is not None:
         t = torch.tensor([ms_step, e2e_ms], device=f"cuda:{local}", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step, e2e_ms = float(t[0]), float(t[1])
+    cpu = parity = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        # the raster-order oracle on one whole image (0.62 TFLOP of scalar fp32 work): a timed CPU baseline that
+        # needs no extrapolation, and a check of the same image's GPU result
+        from juliavision_b200.hiera import init_weights as hiera_weights
+        from oracle import oracle as ora
+        from oracle.hiera_ref import oracle_forward as hiera_oracle
+        cores = ora.use_all_cores()
+        one = Hiera(ctx, cfg, batch=1)
+        ctx.upload(one.image, img[:1])
+        got = one.forward().to_host().astype(np.float64)
+        t0 = time.perf_counter()
+        ref = hiera_oracle(cfg, hiera_weights(cfg), img[:1]).astype(np.float64)
+        dt = time.perf_counter() - t0
+        rel = float(np.max(np.abs(got - ref)) / np.max(np.abs(ref)))
+        cpu = dict(value=round(dt * 1e3, 1), unit="ms/img", cores=cores, kind="port",
+                   sample="one whole 1024x1024 image through all 24 blocks of the raster-order oracle, no extrapolation")
+        parity = dict(rel_err=round(rel, 6), tol=1e-2, ok=bool(rel < 1e-2),
+                      what="the same image through this library and the CPU oracle, max|d|/max|ref| over the 32x32x896 output")
+        del one
     if rank == 0:
         imgs = nb * world
         print(json.dumps(dict(
@@ -436,7 +564,7 @@ def run_hiera(args):
                         imgs_per_step=imgs, tflops_per_gpu=round(cfg.flops(nb) / ms_step / 1e9, 1)),
             e2e=dict(value=round(e2e_ms / imgs, 4), unit="ms/img", h2d_bytes_per_step=int(img.nbytes),
                      d2h_bytes_per_step=int(model.y.nbytes)),
-            gpu_launches=per_pass * args.steps, roofline=None, clocks=clocks, cpu_baseline=None)), flush=True)
+            gpu_launches=per_pass * args.steps, roofline=roofline, clocks=clocks, cpu_baseline=cpu, parity=parity)), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -453,6 +581,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="encoder depth (32 = the named config)")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel figures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--no-sweeps", action="store_true", help="skip the config-5 sweeps (GEMM split along M, 64 images)")
     ap.add_argument("--workload", default="encoder", choices=["encoder", "hiera"],
                     help="encoder = the headline config-3 stack; hiera = the image workload of the scaling sweep")
     ap.add_argument("--images", type=int, default=8, help="images per GPU per step for --workload hiera")
@@ -577,6 +706,10 @@ def main():
     cpu = parity = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu, parity = cpu_baseline(ctx, cfg, weights, x, min(args.cpu_layers, cfg.layers))
+    sweeps = None
+    if not args.no_sweeps:
+        del graph, ggraph, enc          # the encoder's 1.2 GB of weights and its graphs are no longer needed
+        sweeps = config5_sweeps(ctx, jv, world, rank, dist, torch, local, quick=args.steps < 10)
 
     if rank == 0:
         line = dict(
@@ -600,7 +733,7 @@ def main():
                           note="all GEMM launches of one pass, replayed back to back; flops = 2MNK unpadded; "
                                "traffic is a profiler capture (caches flushed before each launch there, so "
                                "activations count as DRAM reads and the outputs stay in L2)"),
-            clocks=clocks, kernels=kernels, cpu_baseline=cpu, parity=parity)
+            clocks=clocks, kernels=kernels, cpu_baseline=cpu, parity=parity, sweeps=sweeps)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

@@ -180,9 +180,35 @@ class Hiera:
         self.ctx.contiguous(v.permute((0, 2, 1, 3)), out=self._view(dst, Cn * w, n, w, n * self.batch))
 
     # ---- one pass
+    def gemm_pass(self) -> None:
+        """Only the projection / MLP GEMM launches of a pass, in pass order and on the pass's own buffers
+        (values are meaningless): what a benchmark replays to time the GEMM family of the pass alone."""
+        self._gemm_only = True
+        try:
+            self.forward()
+        finally:
+            self._gemm_only = False
+
+    def gemm_flops(self) -> float:
+        """2MNK summed over the launches of `gemm_pass` (the stem convolution and attention excluded)."""
+        total = 0.0
+        for b in self.plan:
+            T_in, T = b["side_in"] ** 2, b["side"] ** 2
+            d_in, d = b["dim_in"], b["dim"]
+            total += 2.0 * T_in * d_in * 3 * d + 2.0 * T * d * d + 4.0 * T * d * d * self.cfg.mlp_ratio
+            if b["pool"]:
+                total += 2.0 * T_in * d_in * d
+        return total * self.batch
+
     def forward(self) -> DeviceArray:
         """Encode the images in `self.image` ((W,H,Cin,N), i.e. torch NCHW); the result, torch
         (N, H/32, W/32, 896), lands in `self.y`."""
+        if getattr(self, "_gemm_only", False):
+            x, spare, cur_w = self.xa, self.xb, self.cfg.windows[0]
+            for b, w in zip(self.plan, self.blocks):
+                self.ctx.ws.reset()
+                x, spare, cur_w = self._block(b, w, x, spare, cur_w)
+            return self.y
         ctx, cfg, B = self.ctx, self.cfg, self.batch
         k, s, p = cfg.patch
         S0, d0 = cfg.side(0), cfg.embed
@@ -210,6 +236,7 @@ class Hiera:
     def _block(self, b: dict, w: Dict[str, DeviceArray], x: DeviceArray, spare: DeviceArray, cur_w: int,
                pending: bool = False, defer: bool = False):
         ctx, cfg, B = self.ctx, self.cfg, self.batch
+        every = not getattr(self, "_gemm_only", False)   # False: only the GEMM launches (see gemm_pass)
         d_in, d, H, E = b["dim_in"], b["dim"], b["heads"], cfg.head_dim
         T_in, T = b["side_in"] ** 2 * B, b["side"] ** 2 * B
         Lk = b["window"] ** 2 if b["window"] else b["side_in"] ** 2
@@ -220,7 +247,9 @@ class Hiera:
         h = self._view(self.h, d_in, T_in)
         mean, rstd = DeviceArray(ctx, self.mean.ptr, np.float32, (T_in,), owner=self.mean), \
             DeviceArray(ctx, self.rstd.ptr, np.float32, (T_in,), owner=self.rstd)
-        if pending:      # x += (previous block's MLP output); h = LN1(x)
+        if not every:
+            pass
+        elif pending:      # x += (previous block's MLP output); h = LN1(x)
             add_layernorm_(ctx, h, mean, rstd, xv, self._view(self.tmp, d_in, T_in), w["ln1_g"], w["ln1_b"], d_in, cfg.eps)
         else:
             layernorm_(ctx, h, mean, rstd, xv, w["ln1_g"], w["ln1_b"], d_in, cfg.eps)
@@ -236,10 +265,12 @@ class Hiera:
             pooled = lambda buf: DeviceArray(ctx, buf.ptr, np.float16, (ww // 2, ww // 2, d, nwin),
                                              (d, d * (ww // 2), 1, d * Lq), owner=buf)
             sc_in = DeviceArray(ctx, sc.ptr, np.float16, (ww, ww, d, nwin), (d, d * ww, 1, d * Lk), owner=sc)
-            maxpool2d_(ctx, pooled(spare), sc_in, (2, 2), (2, 2))
+            if every:
+                maxpool2d_(ctx, pooled(spare), sc_in, (2, 2), (2, 2))
             # queries: the q rows of qkv pooled the same way
             q_in = DeviceArray(ctx, qkv.ptr, np.float16, (ww, ww, d, nwin), (3 * d, 3 * d * ww, 1, 3 * d * Lk), owner=qkv)
-            maxpool2d_(ctx, pooled(self.qp), q_in, (2, 2), (2, 2))
+            if every:
+                maxpool2d_(ctx, pooled(self.qp), q_in, (2, 2), (2, 2))
             q = DeviceArray(ctx, self.qp.ptr, np.float16, (E, Lq, H, nwin), (1, d, E, d * Lq), owner=self.qp)
             x_new, spare_new = spare, x            # the pooled shortcut is the new residual stream
         else:
@@ -248,24 +279,26 @@ class Hiera:
             x_new, spare_new = x, spare
         att = self._view(self.att, d, T)
         att_view = DeviceArray(ctx, att.ptr, np.float16, (E, Lq, H, nwin), (1, d, E, d * Lq), owner=att)
-        sdpa(ctx, q, part(1), part(2), None, 1.0 / sqrt(E), out=att_view)
+        if every:
+            sdpa(ctx, q, part(1), part(2), None, 1.0 / sqrt(E), out=att_view)
         o = self._view(self.tmp, d, T)
         matmul_(ctx, o, w["wo"], att, w["bo"])
         xn = self._view(x_new, d, T)
         h2 = self._view(self.h, d, T)
         mean2, rstd2 = DeviceArray(ctx, self.mean.ptr, np.float32, (T,), owner=self.mean), \
             DeviceArray(ctx, self.rstd.ptr, np.float32, (T,), owner=self.rstd)
-        add_layernorm_(ctx, h2, mean2, rstd2, xn, o, w["ln2_g"], w["ln2_b"], d, cfg.eps)        # x += o; h = LN2(x)
+        if every:
+            add_layernorm_(ctx, h2, mean2, rstd2, xn, o, w["ln2_g"], w["ln2_b"], d, cfg.eps)        # x += o; h = LN2(x)
         ff = self._view(self.ff, d * cfg.mlp_ratio, T)
         matmul_(ctx, ff, w["w1"], h2, w["b1"], epi="gelu")
         matmul_(ctx, o, w["w2"], ff, w["b2"])
-        if not defer:
+        if not defer and every:
             add_(ctx, self._view(x_new, d * T), self._view(x_new, d * T), self._view(self.tmp, d * T))
         new_w = cur_w
         if b["pool"]:
             # tokens now sit in the left stage's windows at half the side; move to this stage's windows
             new_w = cfg.windows[b["stage"]]
-            if new_w != cur_w // 2:
+            if new_w != cur_w // 2 and every:
                 self._to_raster(spare_new, x_new, d, b["side"], cur_w // 2)
                 self._to_windows(x_new, spare_new, d, b["side"], new_w)
         return x_new, spare_new, new_w
