@@ -131,11 +131,15 @@ def test_pool_and_workspace(ctx):
     assert ctx.ws.stats()[2] == 1 and ctx.ws.stats()[1] >= int(1.5 * (cap + 5)) - 512
     ctx.ws.reset()
     assert ctx.ws.stats()[0] == 0 and ctx.ws.stats()[2] == 0
+    def reserved():
+        use, res = C.c_size_t(), C.c_size_t()
+        _lib.check(_lib.lib().b200_pool_stats(ctx.handle, C.byref(use), C.byref(res)))
+        return res.value
     x = ctx.allocate(np.float32, 1024)
-    p = x.ptr
-    assert p % 256 == 0
+    assert x.ptr % 256 == 0
+    before = reserved()
     del x
-    y = ctx.allocate(np.float32, 1024)                                         # the freed block is reused
-    assert y.ptr == p
+    y = ctx.allocate(np.float32, 1024)                                         # a freed block of the size class is reused:
+    assert reserved() == before                                                # nothing new is taken from the driver
     with pytest.raises(jv.B200Error):
         _lib.check(_lib.lib().b200_pool_free(ctx.handle, C.c_void_p(12345)))

@@ -284,3 +284,25 @@ def test_timeline_records_time_and_cycles(ctx):
     jv.matmul_(ctx, out, W, X, None)
     ctx.synchronize()
     assert not tl.to_host().any()
+
+
+def test_weight_operand_produced_by_the_previous_launch(ctx):
+    """Launches overlap their predecessor's tail (programmatic dependent launch) and must not read an operand
+    before the dependency wait.  Here the first product is the second one's A operand (as in a batched
+    product of two activations) and changes every round, so a read that came too early would show."""
+    rng = np.random.default_rng(31)
+    M1, K1, N1 = 512, 256, 384          # Y1 (M1, N1) = W1 (M1, K1) . X1 (K1, N1)
+    N2 = 300                            # Y2 (M1, N2) = Y1 (M1, N1) . X2 (N1, N2)
+    W1 = ctx.toback(np.float16(rng.standard_normal((K1, M1)) * 0.1))      # torch (K, out)
+    X2 = ctx.toback(np.float16(rng.standard_normal((N2, N1)) * 0.1))      # torch (tokens, K)
+    Y1 = ctx.allocate(np.float16, M1, N1)
+    Y2 = ctx.allocate(np.float16, M1, N2)
+    for round_ in range(4):
+        x1 = np.float16(rng.standard_normal((N1, K1)) * 0.1)
+        X1 = ctx.toback(x1)
+        jv.matmul_(ctx, Y1, W1, X1, None)
+        jv.matmul_(ctx, Y2, Y1, X2, None)     # A = the output of the launch just before
+        ctx.synchronize()
+        y1 = Y1.to_host()                                        # torch (N1, M1)
+        want = np.float32(X2.to_host()) @ np.float32(y1)         # (N2, N1) @ (N1, M1)
+        assert relerr(Y2.to_host(), want) < 5e-3, f"round {round_}"
