@@ -494,8 +494,8 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         case B200_EPI_RELU: emit([](__half2 t) { return __hmax2(t, __float2half2_rn(0.f)); }); break;
                         case B200_EPI_GELU:
                             emit([](__half2 t) {
-                                const float2 f = __half22float2(t);
-                                return __floats2half2_rn(gelu_exact(f.x), gelu_exact(f.y));
+                                const float2 g = gelu_exact2(__half22float2(t));
+                                return __floats2half2_rn(g.x, g.y);
                             });
                             break;
                         case B200_EPI_GELU_TANH:
