@@ -114,6 +114,21 @@ int b200_fill_bytes(b200_ctx* ctx, void* dst_dev, int byte, size_t bytes);
 int b200_host_alloc(size_t bytes, void** hptr); /* pinned host memory */
 int b200_host_free(void* hptr);
 
+/* The copy lane (new surface, no reference counterpart: the reference uploads with toback and reads results with
+ * Array(), both blocking).  A second stream of the context for pinned-host <-> device copies, so that the input
+ * of the next pass goes up and the result of the previous one comes down while the compute stream runs the
+ * current pass.  Order between the two lanes is what the caller states with events: record an event on one lane,
+ * make the other lane wait for it.  An event may be re-recorded; a wait refers to the record before it.
+ * b200_sync waits for both lanes. */
+enum { B200_LANE_COMPUTE = 0, B200_LANE_COPY = 1 };
+typedef struct b200_event b200_event;
+int b200_copy_lane_upload(b200_ctx* ctx, void* dst_dev, const void* src_pinned_host, size_t bytes);
+int b200_copy_lane_download(b200_ctx* ctx, void* dst_pinned_host, const void* src_dev, size_t bytes);
+int b200_event_create(b200_ctx* ctx, b200_event** out);
+int b200_event_destroy(b200_event* e);
+int b200_event_record(b200_ctx* ctx, b200_event* e, int lane);
+int b200_lane_wait_event(b200_ctx* ctx, int lane, b200_event* e);
+
 /* Per-op bump workspace: Workspace / reset! / scratch! (workspace.jl:19-106).
  * Offsets are 256-byte aligned; growth allocates max(need*1.5, 1 MiB) and RETIRES the
  * old block until the next reset, exactly as the reference does, so pointers handed

@@ -19,6 +19,7 @@ from .rewrites import foldbatchnorm, foldrelu, hoistcasts, weightsource
 from .safetensors import readsafetensors, safetensorsnames
 from .plan import Slab, alignup, checkslab, lifetimes, place, planslab
 from .shard import gather_shards, shard_range, shard_range_py
+from .streaming import Event, StreamedPass
 
 __all__ = [
     "B200Error", "SO_PATH", "lib", "sdpa", "sdpa_", "sdpaplan", "Ctx", "DeviceArray", "DeviceCaps", "Workspace",
@@ -27,4 +28,5 @@ __all__ = [
     "mmplan", "Model", "execute_", "hoistpermutes", "foldgelu", "Buffer", "Graph", "Op", "evalshape", "loadgraph",
     "Slab", "alignup", "checkslab", "lifetimes", "place", "planslab", "shard_range", "shard_range_py", "gather_shards",
     "maxpool2d_", "to_copy_", "MMGemvPlan", "foldoutcasts", "foldincasts", "foldbatchnorm", "foldrelu", "hoistcasts", "weightsource", "readsafetensors", "safetensorsnames",
+    "Event", "StreamedPass",
 ]

@@ -69,6 +69,12 @@ SIGNATURES = {
     "b200_fill_bytes": (_i32, [_vp, _vp, _i32, _sz]),
     "b200_host_alloc": (_i32, [_sz, _pp]),
     "b200_host_free": (_i32, [_vp]),
+    "b200_copy_lane_upload": (_i32, [_vp, _vp, _vp, _sz]),
+    "b200_copy_lane_download": (_i32, [_vp, _vp, _vp, _sz]),
+    "b200_event_create": (_i32, [_vp, _pp]),
+    "b200_event_destroy": (_i32, [_vp]),
+    "b200_event_record": (_i32, [_vp, _vp, _i32]),
+    "b200_lane_wait_event": (_i32, [_vp, _i32, _vp]),
     "b200_workspace_reset": (_i32, [_vp]),
     "b200_workspace_scratch": (_i32, [_vp, _sz, _pp]),
     "b200_workspace_stats": (_i32, [_vp, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_i32)]),

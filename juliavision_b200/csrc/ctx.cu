@@ -229,6 +229,8 @@ int b200_ctx_create(int device, b200_ctx** out) {
     cudaStreamSynchronize(c->stream);
     cudaEventCreate(&c->ev0);
     cudaEventCreate(&c->ev1);
+    e = cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { b200_ctx_destroy(c); return fail_cuda(e, "cudaStreamCreate(copy lane)"); }
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
@@ -245,6 +247,7 @@ int b200_ctx_destroy(b200_ctx* c) {
     if (!c) return B200_OK;
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
+    if (c->copy_stream) { cudaStreamSynchronize(c->copy_stream); cudaStreamDestroy(c->copy_stream); }
     for (b200_graph* g : c->graphs) g->ctx = nullptr;   // a graph destroyed later has nothing left to unpin
     for (auto& kv : c->free_blocks) cudaFree(kv.second);
     for (auto& kv : c->live_blocks) cudaFree(kv.first);
@@ -277,6 +280,7 @@ int b200_caps(b200_ctx* c, b200_caps_t* out) {
 int b200_sync(b200_ctx* c) {
     B200_REQUIRE(c, B200_EINVAL, "sync: null ctx");
     B200_CUDA(cudaStreamSynchronize(c->stream));
+    B200_CUDA(cudaStreamSynchronize(c->copy_stream));
     int st = 0;
     B200_CUDA(cudaMemcpy(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (st != 0) {
@@ -391,6 +395,54 @@ int b200_download_async(b200_ctx* c, void* dst, const void* src, size_t bytes) {
     B200_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream));
     return B200_OK;
 }
+// ---- the copy lane and its events
+static cudaStream_t lane_stream(b200_ctx* c, int lane) { return lane == B200_LANE_COPY ? c->copy_stream : c->stream; }
+
+int b200_copy_lane_upload(b200_ctx* c, void* dst, const void* src, size_t bytes) {
+    B200_REQUIRE(c && (bytes == 0 || (dst && src)), B200_EINVAL, "copy_lane_upload: null argument");
+    if (bytes == 0) return B200_OK;
+    B200_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, c->copy_stream));
+    return B200_OK;
+}
+int b200_copy_lane_download(b200_ctx* c, void* dst, const void* src, size_t bytes) {
+    B200_REQUIRE(c && (bytes == 0 || (dst && src)), B200_EINVAL, "copy_lane_download: null argument");
+    if (bytes == 0) return B200_OK;
+    B200_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->copy_stream));
+    return B200_OK;
+}
+int b200_event_create(b200_ctx* c, b200_event** out) {
+    B200_REQUIRE(c && out, B200_EINVAL, "event_create: null argument");
+    B200_CUDA(cudaSetDevice(c->device));
+    cudaEvent_t ev = nullptr;
+    B200_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    b200_event* e = new b200_event();
+    e->ev = ev;
+    e->device = c->device;
+    *out = e;
+    return B200_OK;
+}
+int b200_event_destroy(b200_event* e) {
+    if (e) {
+        if (e->ev) cudaEventDestroy(e->ev);
+        delete e;
+    }
+    return B200_OK;
+}
+int b200_event_record(b200_ctx* c, b200_event* e, int lane) {
+    B200_REQUIRE(c && e && e->ev, B200_EINVAL, "event_record: null argument");
+    B200_REQUIRE(lane == B200_LANE_COMPUTE || lane == B200_LANE_COPY, B200_EINVAL, "event_record: lane %d", lane);
+    B200_REQUIRE(!(c->capturing && lane == B200_LANE_COMPUTE), B200_EINVAL, "event_record: the compute lane is being captured");
+    B200_CUDA(cudaEventRecord(e->ev, lane_stream(c, lane)));
+    return B200_OK;
+}
+int b200_lane_wait_event(b200_ctx* c, int lane, b200_event* e) {
+    B200_REQUIRE(c && e && e->ev, B200_EINVAL, "lane_wait_event: null argument");
+    B200_REQUIRE(lane == B200_LANE_COMPUTE || lane == B200_LANE_COPY, B200_EINVAL, "lane_wait_event: lane %d", lane);
+    B200_REQUIRE(!(c->capturing && lane == B200_LANE_COMPUTE), B200_EINVAL, "lane_wait_event: the compute lane is being captured");
+    B200_CUDA(cudaStreamWaitEvent(lane_stream(c, lane), e->ev, 0));
+    return B200_OK;
+}
+
 int b200_copy(b200_ctx* c, void* dst, const void* src, size_t bytes) {
     B200_REQUIRE(c && (bytes == 0 || (dst && src)), B200_EINVAL, "copy: null argument");
     if (bytes == 0) return B200_OK;

@@ -53,6 +53,7 @@ struct b200_ctx {
     bool capturing = false;
     unsigned long long* gemm_trace = nullptr;  // device buffer of >= 32 slots while tracing, else null
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaStream_t copy_stream = nullptr;   // the copy lane: host<->device copies that overlap the compute stream
     b200::EncodeTiledFn encode = nullptr;
 
     // cudaMalloc pool: free blocks by size, live blocks by pointer.
@@ -77,6 +78,11 @@ struct b200_ctx {
 
 constexpr int SK_FLAG_COUNT = 4096;
 constexpr int GEMV_COUNTER_COUNT = 4096;   // arrival counters of the split matrix-vector product, after the flags
+
+struct b200_event {
+    cudaEvent_t ev = nullptr;
+    int device = 0;
+};
 
 struct b200_graph {
     cudaGraphExec_t exec = nullptr;
