@@ -10,7 +10,7 @@ from .attention import sdpa, sdpa_, sdpaplan
 from .context import Ctx, DeviceArray, DeviceCaps, Workspace, caps
 from .conv import convolution_, convsize, onebyone
 from .elementwise import act_, add_, clamp_, maxpool2d_, to_copy_
-from .execute import Model, execute_, foldgelu, foldincasts, foldoutcasts, hoistpermutes
+from .execute import Diagnostics, Model, execute_, foldgelu, foldincasts, foldoutcasts, hoistpermutes
 from .graph import Buffer, Graph, Op, evalshape, loadgraph
 from .kernelplans import AttnScalarPlan, Decline, FlashTCPlan, MMGemvPlan, MMScalarPlan, MMTilePlan
 from .layernorm import add_layernorm_, layernorm_, native_layer_norm
@@ -28,5 +28,5 @@ __all__ = [
     "mmplan", "Model", "execute_", "hoistpermutes", "foldgelu", "Buffer", "Graph", "Op", "evalshape", "loadgraph",
     "Slab", "alignup", "checkslab", "lifetimes", "place", "planslab", "shard_range", "shard_range_py", "gather_shards",
     "maxpool2d_", "to_copy_", "MMGemvPlan", "foldoutcasts", "foldincasts", "foldbatchnorm", "foldrelu", "hoistcasts", "weightsource", "readsafetensors", "safetensorsnames",
-    "Event", "StreamedPass",
+    "Event", "StreamedPass", "Diagnostics",
 ]

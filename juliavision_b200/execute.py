@@ -14,8 +14,9 @@ An op outside this set raises, as `runop!`'s fallback does (execute.jl:541-542).
 from __future__ import annotations
 
 import copy
+from dataclasses import dataclass
 from math import sqrt
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 
@@ -188,6 +189,31 @@ def foldincasts(graph: Graph) -> int:
     return n
 
 
+# ------------------------------------------------------------------------------ diagnostics
+@dataclass
+class Diagnostics:
+    """Measurements a run writes into, all off by default (context.jl:162-221).
+
+    optimes         aten name -> (count, milliseconds): every op bracketed by CUDA events on the context's
+                    stream with a synchronise around it — a serialising measurement, the only kind that
+                    attributes device time to a source-level op, so the totals run longer than the pass.
+    opdouble        name of an aten op to run twice per pass ("*" = every op, together with opdoublefilter);
+                    the pass's time then grows by that op's real cost in situ, with nothing else disturbed.
+    opdoublefilter  (op) -> bool narrowing opdouble to one shape or call site.
+    planmisses      buffer id -> count of destinations the slab plan could not place (allocated from the pool).
+    launches        aten name -> (ops, kernel launches): which source-level op costs how many launches.
+    """
+    optimes: Optional[Dict[str, Tuple[int, float]]] = None
+    opdouble: str = ""
+    opdoublefilter: Optional[Callable[[Any], bool]] = None
+    planmisses: Optional[Dict[str, int]] = None
+    launches: Optional[Dict[str, Tuple[int, int]]] = None
+
+    def table(self) -> List[Tuple[str, int, float]]:
+        """optimes as (aten, count, ms), slowest first."""
+        return sorted(((k, n, ms) for k, (n, ms) in (self.optimes or {}).items()), key=lambda r: -r[2])
+
+
 # ------------------------------------------------------------------------------ model
 class Model:
     """Model(graph, weights): rewrite, upload, plan (driver.jl:128-182). `weights` maps safetensors
@@ -215,6 +241,7 @@ class Model:
         self.plan: Optional[Slab] = planslab(self.graph, self.dims) if plan else None
         self.slab = ctx.allocate(np.uint8, max(self.plan.bytes, 256)) if self.plan else None       # scratchfor
         self.planmisses: Dict[str, int] = {}
+        self.diag = Diagnostics(planmisses=self.planmisses)     # m.diag.optimes = {} instruments the next calls
 
     def __call__(self, *inputs):
         """call(m, name, x...) (driver.jl:202-223): returns the graph's outputs as device arrays."""
@@ -222,7 +249,7 @@ class Model:
         for id, x in zip(self.graph.inputs, inputs):
             ins[id] = x if isinstance(x, DeviceArray) else self.ctx.toback(np.ascontiguousarray(x))
         return execute_(self.ctx, self.graph, ins, self.weights, dims=self.dims, plan=self.plan, slab=self.slab,
-                        planmisses=self.planmisses)
+                        planmisses=self.planmisses, diag=self.diag)
 
 
 # ------------------------------------------------------------------------------ execution
@@ -453,18 +480,39 @@ RUNOP = {
 
 def execute_(ctx: Ctx, graph: Graph, inputs: Dict[str, DeviceArray], weights: Dict[str, DeviceArray],
              dims: Optional[Dict[str, int]] = None, plan: Optional[Slab] = None, slab: Optional[DeviceArray] = None,
-             planmisses: Optional[Dict[str, int]] = None) -> List[Any]:
-    """execute!(graph, inputs, weights; slab, plan, ws) (execute.jl:493-539): run the ops in order,
-    resetting the workspace at the top of each; nothing synchronises between ops."""
+             planmisses: Optional[Dict[str, int]] = None, diag: Optional[Diagnostics] = None) -> List[Any]:
+    """execute!(graph, inputs, weights; slab, plan, ws, diag) (execute.jl:493-539): run the ops in order,
+    resetting the workspace at the top of each; nothing synchronises between ops unless `diag.optimes` asks
+    for per-op times (timeop!, execute.jl:550-570)."""
     env: Dict[str, Any] = {}
     env.update(weights)
     env.update(inputs)
+    diag = diag or Diagnostics()
+    if planmisses is None:
+        planmisses = diag.planmisses
     run = _Run(ctx, graph, env, dims or {}, plan, slab, planmisses)
     for op in graph.ops:
         run.outid = op.out
-        ctx.ws.reset()
         fn = RUNOP.get(op.aten)
         if fn is None:
             raise B200Error(1, f"no B200 implementation for {op.aten} (op {op.id})")
-        env[op.out] = fn(run, op)
+        n0 = ctx.launch_count() if diag.launches is not None else 0
+        if diag.optimes is not None:
+            ctx.synchronize()
+            ctx.ws.reset()
+            ctx.timer_start()
+            env[op.out] = fn(run, op)
+            ms = ctx.timer_stop()          # records, synchronises, reads
+            n, tot = diag.optimes.get(op.aten, (0, 0.0))
+            diag.optimes[op.aten] = (n + 1, tot + ms)
+        else:
+            d = diag.opdouble
+            if d and (d == "*" or op.aten == d) and (diag.opdoublefilter is None or diag.opdoublefilter(op)):
+                ctx.ws.reset()
+                fn(run, op)                # an idempotent op run a second time changes nothing but the pass's time
+            ctx.ws.reset()
+            env[op.out] = fn(run, op)
+        if diag.launches is not None:
+            n, k = diag.launches.get(op.aten, (0, 0))
+            diag.launches[op.aten] = (n + 1, k + ctx.launch_count() - n0)
     return [run.value(o) for o in graph.outputs]

@@ -167,3 +167,42 @@ def test_streamed_passes_give_each_input_its_own_result(ctx):
         assert np.array_equal(got, want[i]), f"pass {i}"
     for p_ in hin + hout:
         _lib.lib().b200_host_free(C.c_void_p(p_))
+
+
+def test_diagnostics_time_ops_without_changing_values(ctx):
+    """Per-op times (a serialising measurement), launches per op, and an op run twice in situ: the values of
+    the pass do not change, every aten of the graph is in the table, and the counts are the graph's."""
+    import json
+
+    from juliavision_b200.encoder_graph import encoder_graph
+    from juliavision_b200.execute import Model
+    from juliavision_b200.graph import loadgraph
+    cfg = EncoderConfig(layers=2, d_model=256, heads=4, ffn=1024, tokens=300)
+    w = init_weights(cfg)
+    x = np.float16(np.random.default_rng(9).standard_normal((cfg.tokens, cfg.d_model)))
+    g, wts = encoder_graph(cfg, w)
+    model = Model(ctx, loadgraph(json.loads(json.dumps(g))), wts)
+    (plain,) = model(x.reshape(1, cfg.tokens, cfg.d_model))
+    ctx.synchronize()
+    plain = plain.to_host()
+    model.diag.optimes, model.diag.launches = {}, {}
+    (timed,) = model(x.reshape(1, cfg.tokens, cfg.d_model))
+    ctx.synchronize()
+    assert np.array_equal(timed.to_host(), plain)
+    atens = {op.aten for op in model.graph.ops}
+    assert set(model.diag.optimes) == atens == set(model.diag.launches)
+    counts = {a: sum(op.aten == a for op in model.graph.ops) for a in atens}
+    assert {a: n for a, (n, _) in model.diag.optimes.items()} == counts
+    assert all(ms > 0 for _, _, ms in model.diag.table())
+    assert model.diag.launches["addmm.default"][1] >= counts["addmm.default"]
+    model.diag.optimes = model.diag.launches = None
+    model.diag.opdouble = "addmm.default"
+    n0 = ctx.launch_count()
+    (doubled,) = model(x.reshape(1, cfg.tokens, cfg.d_model))
+    ctx.synchronize()
+    assert np.array_equal(doubled.to_host(), plain)
+    model.diag.opdouble = ""
+    n1 = ctx.launch_count()
+    model(x.reshape(1, cfg.tokens, cfg.d_model))
+    ctx.synchronize()
+    assert (n1 - n0) - (ctx.launch_count() - n1) == counts["addmm.default"]     # one extra launch per doubled op
