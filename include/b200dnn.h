@@ -223,6 +223,12 @@ int b200_attention_f16_supported(int64_t E, int64_t Lq, int64_t Lk, int64_t H, i
                                  const int64_t* qstride, const int64_t* kstride,
                                  const int64_t* vstride, int has_bias);
 
+/* Which way a call will run: 0 the fused tensor-core kernel (FlashCMPlan's place), 1 two batched GEMMs with a
+ * softmax between them (sdpa_coopmat! + attn_softmax_rows!, attention.jl:528-705: head dims 136..4096 in
+ * multiples of 8, E contiguous), 2 the scalar kernel.  Every route takes the additive mask. */
+int b200_attention_f16_route(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B, const int64_t* qstride,
+                             const int64_t* kstride, const int64_t* vstride);
+
 /* ------------------------------------------------------------------- layer norm */
 /*
  * layernorm!/layernorm_kernel! (layernorm.jl:44-135): a is (C, groups) contiguous,

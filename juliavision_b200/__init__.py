@@ -12,7 +12,7 @@ from .conv import convolution_, convsize, onebyone
 from .elementwise import act_, add_, clamp_, maxpool2d_, to_copy_
 from .execute import Diagnostics, Model, execute_, foldgelu, foldincasts, foldoutcasts, hoistpermutes
 from .graph import Buffer, Graph, Op, evalshape, loadgraph
-from .kernelplans import AttnScalarPlan, Decline, FlashTCPlan, MMGemvPlan, MMScalarPlan, MMTilePlan
+from .kernelplans import AttnScalarPlan, Decline, FlashTCPlan, MMGemvPlan, MMScalarPlan, MMTilePlan, TwoGemmPlan
 from .layernorm import add_layernorm_, layernorm_, native_layer_norm
 from .matmul import batchedmatmul_, matmul_, mmplan
 from .rewrites import foldbatchnorm, foldrelu, hoistcasts, weightsource
@@ -28,5 +28,5 @@ __all__ = [
     "mmplan", "Model", "execute_", "hoistpermutes", "foldgelu", "Buffer", "Graph", "Op", "evalshape", "loadgraph",
     "Slab", "alignup", "checkslab", "lifetimes", "place", "planslab", "shard_range", "shard_range_py", "gather_shards",
     "maxpool2d_", "to_copy_", "MMGemvPlan", "foldoutcasts", "foldincasts", "foldbatchnorm", "foldrelu", "hoistcasts", "weightsource", "readsafetensors", "safetensorsnames",
-    "Event", "StreamedPass", "Diagnostics",
+    "Event", "StreamedPass", "Diagnostics", "TwoGemmPlan",
 ]

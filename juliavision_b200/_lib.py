@@ -92,6 +92,7 @@ SIGNATURES = {
                                        C.POINTER(Strided4), C.POINTER(Strided4), C.POINTER(Strided4), _i32, _f32]),
     "b200_attention_f16_supported": (_i32, [_i64, _i64, _i64, _i64, _i64, C.POINTER(_i64), C.POINTER(_i64),
                                             C.POINTER(_i64), _i32]),
+    "b200_attention_f16_route": (_i32, [_i64, _i64, _i64, _i64, _i64, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
     "b200_layernorm": (_i32, [_vp, _i64, _i64, _vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _f32]),
     "b200_add_layernorm_f16": (_i32, [_vp, _i64, _i64, _vp, _vp, _i32, _f32, _f32, _vp, _vp, _vp, _vp, _vp, _f32]),
     "b200_im2col_f16": (_i32, [_vp] + [_i64] * 14 + [_vp, _vp]),

@@ -17,7 +17,7 @@ import numpy as np
 from . import _lib
 from ._lib import B200Error, check
 from .context import Ctx, DeviceArray, dtcode
-from .kernelplans import AttnScalarPlan, Decline, FlashTCPlan
+from .kernelplans import AttnScalarPlan, Decline, FlashTCPlan, TwoGemmPlan
 
 
 def _s4(a: DeviceArray) -> "_lib.Strided4":
@@ -49,6 +49,8 @@ def sdpaplan(ctx: Ctx, q: DeviceArray, k: DeviceArray, v: DeviceArray, bias=None
         return FlashTCPlan(EP=64 if E <= 64 else 128)
     if any(a.strides[0] != 1 and a.shape[0] != 1 for a in (q, k, v)):
         return Decline("wrapped")  # E must be contiguous; densify first (attention.jl:734-759)
+    if _lib.lib().b200_attention_f16_route(E, Lq, Lk, H, B, arr(q), arr(k), arr(v)) == 1:
+        return TwoGemmPlan(nbatch=H * B)
     if rc in (_lib.OK, 18, 21):
         return AttnScalarPlan(_lib.DECLINE.get(rc, "wrapped"))
     return Decline(_lib.DECLINE.get(rc, "extent"))

@@ -677,6 +677,104 @@ __global__ void attention_f16_scalar_kernel(int E, int Lq, int Lk, int H, int B,
     }
 }
 
+// ----------------------------------------------------------------------- the two-GEMM route
+// Attention as two batched tensor-core GEMMs with a softmax between them, for head dims the fused kernel's
+// tensor memory cannot hold (E > 128): S(Lk, Lq) = Kt(Lk, E) . Q(E, Lq) in fp32, P = softmax over the keys
+// (fp16, already divided by the row sum), O(E, Lq) = V(E, Lk) . P(Lk, Lq) written straight into out.  The
+// reference's second tier, sdpa_coopmat! + attn_softmax_rows! (attention.jl:528-705), restated for this
+// GEMM's orientation: only K is transposed (one permuted copy), Q and V are read through their strides, and
+// the scores keep the keys contiguous so that the softmax reads and writes whole rows.
+//
+// One warp per (query, head*batch) column of S: scale (+ additive mask), maximum, exponentials, sum, P.  A
+// column whose keys are all blocked comes out as zeros (attn_softmax, attention.jl:73-100).
+__global__ void __launch_bounds__(256)
+attn_softmax_cols_kernel(const float* __restrict__ S, __half* __restrict__ P, int Lk, int64_t ldS, int CH, int64_t ncols,
+                         float scale, const __half* __restrict__ bias, int64_t bsK, int64_t bsQ, int64_t bsH, int64_t bsB,
+                         int q0, int Lq, int H) {
+    const int lane = threadIdx.x & 31;
+    const int64_t col = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // lq_local + CH * hb
+    if (col >= ncols) return;
+    const int lq = q0 + (int)(col % CH);
+    if (lq >= Lq) return;   // a short last chunk: the columns past it hold an earlier chunk's scores and are not used
+    const int hb = (int)(col / CH);
+    const float* s = S + col * ldS;
+    __half* p = P + col * ldS;
+    const __half* bp = bias ? bias + (int64_t)lq * bsQ + (int64_t)(hb % H) * bsH + (int64_t)(hb / H) * bsB : nullptr;
+    float m = -INFINITY;
+    for (int k = lane; k < Lk; k += 32) {
+        float a = s[k] * scale;
+        if (bp) a += __half2float(bp[(int64_t)k * bsK]);
+        m = fmaxf(m, a);
+    }
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (m == -INFINITY) m = 0.f;
+    float l = 0.f;
+    for (int k = lane; k < Lk; k += 32) {
+        float a = s[k] * scale;
+        if (bp) a += __half2float(bp[(int64_t)k * bsK]);
+        l += __expf(a - m);
+    }
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    const float inv = 1.0f / (l == 0.f ? 1.0f : l);
+    for (int k = lane; k < Lk; k += 32) {
+        float a = s[k] * scale;
+        if (bp) a += __half2float(bp[(int64_t)k * bsK]);
+        p[k] = __float2half_rn(__expf(a - m) * inv);
+    }
+}
+
+static int attention_two_gemm(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
+                              const b200_strided4* q, const b200_strided4* k, const b200_strided4* v,
+                              const __half* bias, const int64_t* bs, const b200_strided4* o, int out_dtype, float scale) {
+    const int64_t HB = H * B;
+    const size_t osz = out_dtype == B200_F16 ? 2 : 4;
+    int rc;
+    // Kt(Lk, E, H, B), dense: the one layout pass of this route (the reference transposes Q and V as well)
+    void* kT = nullptr;
+    if ((rc = ws_scratch(ctx, (size_t)(Lk * E * HB) * 2, &kT))) return rc;
+    {
+        const int64_t shape[4] = {Lk, E, H, B};
+        const int64_t stride[4] = {k->stride[1], 1, k->stride[2], k->stride[3]};
+        if ((rc = b200_permute4(ctx, k->ptr, kT, shape, stride, 2))) return rc;
+    }
+    // Queries are taken in chunks so that the fp32 scores and the fp16 probabilities stay within ~256 MB.
+    int64_t CH = (int64_t)(256ll << 20) / (Lk * HB * 6);
+    if (CH > Lq) CH = Lq;
+    CH = CH / 8 * 8;
+    if (CH < 8) CH = Lq < 8 ? Lq : 8;
+    void *S = nullptr, *P = nullptr;
+    if ((rc = ws_scratch(ctx, (size_t)(Lk * CH * HB) * 4, &S))) return rc;
+    if ((rc = ws_scratch(ctx, (size_t)(Lk * CH * HB) * 2, &P))) return rc;
+    // One batched launch over (h, b) when the operands' head and batch strides fold into one, else one per image.
+    auto folds = [&](const b200_strided4* t) { return B == 1 || t->stride[3] == H * t->stride[2]; };
+    const bool one = folds(q) && folds(v) && folds(o);
+    const int64_t nb = one ? HB : H, reps = one ? 1 : B;
+    for (int64_t q0 = 0; q0 < Lq; q0 += CH) {
+        const int64_t n = Lq - q0 < CH ? Lq - q0 : CH;
+        for (int64_t r = 0; r < reps; ++r) {
+            const __half* qp = (const __half*)q->ptr + q0 * q->stride[1] + r * q->stride[3];
+            if ((rc = gemm_f16_run(ctx, Lk, n, E, (const __half*)kT + r * H * Lk * E, Lk, qp, q->stride[1], nullptr, 0,
+                                   (float*)S + r * H * Lk * CH, Lk, B200_F32, B200_EPI_NONE, nb, Lk * E, q->stride[2],
+                                   Lk * CH)))
+                return rc;
+        }
+        const int64_t ncols = CH * HB;
+        attn_softmax_cols_kernel<<<(unsigned)cdiv(ncols, 8), 256, 0, ctx->stream>>>(
+            (const float*)S, (__half*)P, (int)Lk, Lk, (int)CH, ncols, scale, bias, bs[0], bs[1], bs[2], bs[3], (int)q0, (int)Lq,
+            (int)H);
+        ctx->launches++;
+        B200_CUDA(cudaGetLastError());
+        for (int64_t r = 0; r < reps; ++r) {
+            const __half* vp = (const __half*)v->ptr + r * v->stride[3];
+            char* op = (char*)const_cast<void*>(o->ptr) + (size_t)(q0 * o->stride[1] + r * o->stride[3]) * osz;
+            if ((rc = gemm_f16_run(ctx, E, n, Lk, vp, v->stride[1], (const __half*)P + r * H * Lk * CH, Lk, nullptr, 0, op,
+                                   o->stride[1], out_dtype, B200_EPI_NONE, nb, v->stride[2], Lk * CH, o->stride[2])))
+                return rc;
+        }
+    }
+    return B200_OK;
+}
+
 static int tc_reason(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B, const int64_t* qs,
                      const int64_t* ks, const int64_t* vs) {
     if (E < 1 || Lq < 1 || Lk < 1 || H < 1 || B < 1) return B200_DECLINE_EXTENT;
@@ -723,6 +821,18 @@ int b200_attention_f16_supported(int64_t E, int64_t Lq, int64_t Lk, int64_t H, i
     (void)has_bias;   // an additive mask no longer declines: b200_attention_f16_bias takes it
     if (!qstride || !kstride || !vstride) return B200_EINVAL;
     return tc_reason(E, Lq, Lk, H, B, qstride, kstride, vstride);
+}
+
+int b200_attention_f16_route(int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B, const int64_t* qstride,
+                             const int64_t* kstride, const int64_t* vstride) {
+    if (!qstride || !kstride || !vstride) return -1;
+    if (tc_reason(E, Lq, Lk, H, B, qstride, kstride, vstride) == B200_OK) return 0;
+    // Two batched GEMMs and a softmax: head dims past the fused kernel's, when the GEMM's tensor maps can take the
+    // operands as they lie (E contiguous and a multiple of 8) and the problem is worth three launches.
+    if (E > 128 && E % 8 == 0 && E <= 4096 && Lq >= 1 && Lk >= 1 && H >= 1 && B >= 1 && Lk < (1ll << 31) && Lq < (1ll << 31) &&
+        qstride[0] == 1 && kstride[0] == 1 && vstride[0] == 1 && Lq * Lk >= 64 * 64)
+        return 1;
+    return 2;
 }
 
 int b200_attention_f16(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, int64_t H, int64_t B,
@@ -773,6 +883,9 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     const bool tc = tc_reason(E, Lq, Lk, H, B, q->stride, k->stride, v->stride) == B200_OK && al16(q->ptr) &&
                     al16(k->ptr) && al16(v->ptr) && al16(out) && oaligned && scale > 0.f;
+    if (!tc && b200_attention_f16_route(E, Lq, Lk, H, B, q->stride, k->stride, v->stride) == 1 && scale > 0.f &&
+        o->stride[1] > 0 && o->stride[2] > 0 && o->stride[3] > 0)
+        return attention_two_gemm(ctx, E, Lq, Lk, H, B, q, k, v, bptr, bs, o, out_dtype, scale);
     if (!tc) {
         B200_REQUIRE(E <= 1024, B200_DECLINE_EXTENT, "attention: E = %lld", (long long)E);
         const int wpb = 4;

@@ -58,6 +58,14 @@ class FlashTCPlan:
 
 
 @dataclass(frozen=True)
+class TwoGemmPlan:
+    """Attention as two batched tensor-core GEMMs with a row softmax between them; stands where
+    CoopMatSDPAPlan(chunk, EP, nbatch) stood (sdpa_coopmat!, attention.jl:585-705): head dims the fused
+    kernel's tensor memory cannot hold (E > 128).  Only K is copied (transposed); scores in fp32."""
+    nbatch: int = 1
+
+
+@dataclass(frozen=True)
 class AttnScalarPlan:
     """Fused attention for head dims / strides the tensor-core kernel declines."""
     reason: str

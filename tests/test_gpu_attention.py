@@ -116,12 +116,64 @@ def test_sam2_global_shape_head_dim_72_sampled_rows(ctx, ora):
     assert relerr(got[:, :, rows], ref) < TOL, describe(got[:, :, rows], ref, TOL)
 
 
-def test_head_dim_beyond_two_swizzle_rows_takes_the_scalar_kernel(ctx, ora):
+# (B, H, Lq, Lk, E), mask shape or None: head dims past the fused kernel's run as two batched GEMMs and a softmax
+TWO_GEMM = [((1, 2, 300, 264, 256), None), ((2, 3, 128, 512, 136), None), ((1, 2, 100, 77, 160), None),   # Lk = 77: unaligned scores
+            ((2, 2, 200, 200, 192), (2, 1, 200, 200)), ((1, 4, 1030, 520, 256), None)]
+
+
+@pytest.mark.parametrize("shape,bshape", TWO_GEMM)
+def test_head_dims_above_128_run_as_two_gemms_and_a_softmax(ctx, ora, shape, bshape):
+    """sdpa_coopmat! + attn_softmax_rows! (attention.jl:528-705): S = Kt Q in fp32, P = softmax over the keys in fp16,
+    O = V P; against the fp32 reference at the fused kernel's tolerance and the three-pass form at 1e-2; with and
+    without the additive mask (whose all-blocked rows come out as zeros)."""
+    B, H, Lq, Lk, E = shape
+    rng = np.random.default_rng(sum(shape))
+    q = np.float16(rng.standard_normal((B, H, Lq, E)) * 0.3)
+    k = np.float16(rng.standard_normal((B, H, Lk, E)) * 0.3)
+    v = np.float16(rng.standard_normal((B, H, Lk, E)) * 0.3)
+    bias = None
+    if bshape is not None:
+        bias = np.float16(rng.standard_normal(bshape))
+        bias[rng.random(bshape) < 0.3] = -np.inf
+        bias[:, :, 5, :] = -np.inf
+    scale = 1 / np.sqrt(E)
+    for out_dtype in (np.float16, np.float32):
+        got, plan = attention_gpu(ctx, q, k, v, scale, out_dtype, bias=bias)
+        assert isinstance(plan, jv.TwoGemmPlan), plan
+        assert np.all(np.isfinite(got))
+        ref = ora.attention_ref(q, k, v, scale, bias=bias)
+        assert relerr(got, ref) < TOL, describe(got, ref, TOL)
+        if bias is not None:
+            assert np.all(got[:, :, 5] == 0)
+
+
+def test_two_gemm_route_with_heads_interleaved_in_the_token_row(ctx, ora):
+    """q, k, v as views of one (tokens, 3 d) projection and the result token-major: the head and batch strides do not
+    fold into one, so the route runs one batched launch per image; values are those of the dense call."""
+    from .gpu_helpers import qkv_views
+    rng = np.random.default_rng(77)
+    B, H, L, E = 2, 2, 160, 136
+    d = H * E
+    qkv = np.float16(rng.standard_normal((B, L, 3, H, E)) * 0.3)
+    q, k, v = (qkv[:, :, i].transpose(0, 2, 1, 3) for i in range(3))     # (B, H, L, E) strided views
+    dq, dk, dv = qkv_views(ctx, q, k, v)
+    assert isinstance(jv.sdpaplan(ctx, dq, dk, dv), jv.TwoGemmPlan)
+    buf = ctx.allocate(np.float16, d, L, B)
+    ctx.fill_bytes(buf, 0xFF)
+    view = jv.DeviceArray(ctx, buf.ptr, np.float16, (E, L, H, B), (1, d, E, d * L), owner=buf)
+    jv.sdpa(ctx, dq, dk, dv, None, 1 / np.sqrt(E), out=view)
+    ctx.synchronize()
+    got = buf.to_host().reshape(B, L, H, E).transpose(0, 2, 1, 3)
+    ref = ora.attention_ref(np.ascontiguousarray(q), np.ascontiguousarray(k), np.ascontiguousarray(v), 1 / np.sqrt(E))
+    assert relerr(got, ref) < TOL, describe(got, ref, TOL)
+
+
+def test_head_dim_not_a_multiple_of_eight_takes_the_scalar_kernel(ctx, ora):
     rng = np.random.default_rng(12)
-    q, k, v = (np.float16(rng.standard_normal((1, 2, 64, 136)) * 0.2) for _ in range(3))
-    got, plan = attention_gpu(ctx, q, k, v, 1 / np.sqrt(136), np.float32)
+    q, k, v = (np.float16(rng.standard_normal((1, 2, 64, 132)) * 0.2) for _ in range(3))
+    got, plan = attention_gpu(ctx, q, k, v, 1 / np.sqrt(132), np.float32)
     assert isinstance(plan, jv.AttnScalarPlan)
-    assert relerr(got, ora.attention_ref(q, k, v, 1 / np.sqrt(136))) < TOL
+    assert relerr(got, ora.attention_ref(q, k, v, 1 / np.sqrt(132))) < TOL
 
 
 # torch (B,H,Lq,Lk,E) and the bias shape as torch (B|1, H|1, Lq|1, Lk|1)
@@ -131,7 +183,7 @@ BIAS_CASES = [((2, 3, 256, 384, 64), (2, 3, 256, 384)),    # full mask, rows rea
               ((1, 2, 130, 257, 32), (1, 1, 130, 257)),    # broadcast over heads, odd row stride
               ((1, 2, 64, 64, 72), (1, 2, 64, 64)),        # head dim past one swizzle row: two atoms along E
               ((2, 2, 300, 260, 96), (2, 1, 300, 260)),
-              ((1, 1, 40, 40, 136), (1, 1, 40, 40))]       # past two: scalar kernel
+              ((1, 1, 40, 40, 132), (1, 1, 40, 40))]       # not a multiple of 8: scalar kernel
 
 
 @pytest.mark.parametrize("shape,bshape", BIAS_CASES)
