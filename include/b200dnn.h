@@ -271,6 +271,25 @@ int b200_conv2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N,
                     int64_t dx, int64_t dy, const void* x, const void* w, const void* bias,
                     void* out, int out_dtype, int epilogue);
 
+/* The same with groups >= 1 (conv.jl:26-51,100-145; the reference runs grouped convolutions on its direct kernel):
+ * w is (KW,KH,Cin/groups,Cout); each group is lowered like the ungrouped convolution, on its own channel slices. */
+int b200_conv2d_grouped_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW,
+                            int64_t KH, int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py,
+                            int64_t dx, int64_t dy, int64_t groups, const void* x, const void* w, const void* bias,
+                            void* out, int out_dtype, int epilogue);
+/*
+ * convolutiontranspose! (conv.jl:247-290): x (W,H,Cin,N), w (KW,KH,Cout/groups,Cin) — the transposed weight carries
+ * its channel axes the other way round — out (OW,OH,Cout,N) with OW = (W-1)*sx - 2*px + dx*(KW-1) + opx + 1.  The
+ * non-overlapping case (stride equal to the kernel, no padding, dilation or output padding, one group: shufflecase,
+ * conv.jl:219-222) is a GEMM over (W*H) x Cin x (KW*KH*Cout) followed by the depth-to-space scatter (shuffleout,
+ * conv.jl:232-246); everything else is the deterministic gather (convtranspose2d, conv.jl:147-190).  Scratch comes
+ * from the context's workspace.
+ */
+int b200_convtranspose2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW,
+                             int64_t KH, int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py,
+                             int64_t dx, int64_t dy, int64_t opx, int64_t opy, int64_t groups, const void* x,
+                             const void* w, const void* bias, void* out, int out_dtype);
+
 /*
  * The same convolution for callers that must not allocate device memory when they call: a
  * server whose own allocator took the whole GPU at start-up, or a loop that may not make a

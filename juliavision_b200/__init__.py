@@ -8,7 +8,7 @@ is no fallback if the library is missing.
 from ._lib import B200Error, SO_PATH, lib
 from .attention import sdpa, sdpa_, sdpaplan
 from .context import Ctx, DeviceArray, DeviceCaps, Workspace, caps
-from .conv import convolution_, convsize, onebyone
+from .conv import convolution_, convolutiontranspose_, convsize, convtransposesize, onebyone, shufflecase
 from .elementwise import act_, add_, clamp_, maxpool2d_, to_copy_
 from .execute import Diagnostics, Model, execute_, foldgelu, foldincasts, foldoutcasts, hoistpermutes
 from .graph import Buffer, Graph, Op, evalshape, loadgraph
@@ -28,5 +28,5 @@ __all__ = [
     "mmplan", "Model", "execute_", "hoistpermutes", "foldgelu", "Buffer", "Graph", "Op", "evalshape", "loadgraph",
     "Slab", "alignup", "checkslab", "lifetimes", "place", "planslab", "shard_range", "shard_range_py", "gather_shards",
     "maxpool2d_", "to_copy_", "MMGemvPlan", "foldoutcasts", "foldincasts", "foldbatchnorm", "foldrelu", "hoistcasts", "weightsource", "readsafetensors", "safetensorsnames",
-    "Event", "StreamedPass", "Diagnostics", "TwoGemmPlan",
+    "Event", "StreamedPass", "Diagnostics", "TwoGemmPlan", "convolutiontranspose_", "convtransposesize", "shufflecase",
 ]

@@ -97,6 +97,8 @@ SIGNATURES = {
     "b200_add_layernorm_f16": (_i32, [_vp, _i64, _i64, _vp, _vp, _i32, _f32, _f32, _vp, _vp, _vp, _vp, _vp, _f32]),
     "b200_im2col_f16": (_i32, [_vp] + [_i64] * 14 + [_vp, _vp]),
     "b200_conv2d_f16": (_i32, [_vp] + [_i64] * 13 + [_vp, _vp, _vp, _vp, _i32, _i32]),
+    "b200_conv2d_grouped_f16": (_i32, [_vp] + [_i64] * 14 + [_vp, _vp, _vp, _vp, _i32, _i32]),
+    "b200_convtranspose2d_f16": (_i32, [_vp] + [_i64] * 16 + [_vp, _vp, _vp, _vp, _i32]),
     "b200_conv2d_f16_noalloc": (_i32, [_vp] + [_i64] * 13 + [_vp, _vp, _vp, _vp, _i32, _i32]),
     "b200_add_f16": (_i32, [_vp, _vp, _vp, _vp, _i64]),
     "b200_clamp_f16": (_i32, [_vp, _vp, _vp, _i64, _f32, _f32]),

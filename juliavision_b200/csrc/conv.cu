@@ -105,16 +105,13 @@ int b200_im2col_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N,
     return B200_OK;
 }
 
-int b200_conv2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW, int64_t KH,
-                    int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py, int64_t dx, int64_t dy,
-                    const void* x, const void* w, const void* bias, void* out, int out_dtype, int epilogue) {
-    B200_REQUIRE(ctx && x && w && out, B200_EINVAL, "conv2d: null argument");
-    B200_REQUIRE(W > 0 && H > 0 && Cin > 0 && N > 0 && KW > 0 && KH > 0 && Cout > 0 && sx > 0 && sy > 0 &&
-                     dx > 0 && dy > 0 && px >= 0 && py >= 0,
-                 B200_EINVAL, "conv2d: bad geometry");
+// One group of a convolution: Cin_g input channels starting at x (image n at x + n * x_img), Cout_g output
+// channels starting at out (image n at out + n * out_img elements), weight (KW,KH,Cin_g,Cout_g) dense.
+static int conv2d_group(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW, int64_t KH,
+                        int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py, int64_t dx, int64_t dy,
+                        const __half* x, int64_t x_img, const void* w, const void* bias, void* out, int64_t out_img,
+                        int out_dtype, int epilogue) {
     const int64_t OW = convsize(W, KW, sx, px, dx), OH = convsize(H, KH, sy, py, dy);
-    B200_REQUIRE(OW > 0 && OH > 0, B200_DECLINE_EXTENT, "conv2d: empty output");
-    B200_CUDA(cudaSetDevice(ctx->device));
     const int64_t P = OW * OH;       // pixels per image = GEMM M (contiguous in out)
     const int64_t CRS = KW * KH * Cin;
     const size_t osz = out_dtype == B200_F16 ? 2 : 4;
@@ -137,8 +134,8 @@ int b200_conv2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N,
     }
     if (onebyone) {
         for (int64_t n = 0; n < N; ++n) {
-            const __half* xa = (const __half*)x + n * P * Cin; // (P, Cin) ld = P
-            void* on = (char*)out + (size_t)(n * P * Cout) * osz;
+            const __half* xa = x + n * x_img; // (P, Cin) ld = P
+            void* on = (char*)out + (size_t)(n * out_img) * osz;
             if ((rc = gemm_f16_run(ctx, P, Cout, Cin, xa, P, wB, ldw, bias, 1, on, P, out_dtype, epilogue, 1, 0, 0, 0)))
                 return rc;
         }
@@ -148,12 +145,186 @@ int b200_conv2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N,
     void* col = nullptr;
     if ((rc = ws_scratch(ctx, (size_t)(MP * CRS) * 2, &col))) return rc;
     for (int64_t n = 0; n < N; ++n) {
-        const __half* xn = (const __half*)x + n * W * H * Cin;
+        const __half* xn = x + n * x_img;
         if ((rc = b200_im2col_f16(ctx, W, H, Cin, 1, KW, KH, sx, sy, px, py, dx, dy, MP, CRS, xn, col))) return rc;
-        void* on = (char*)out + (size_t)(n * P * Cout) * osz;
+        void* on = (char*)out + (size_t)(n * out_img) * osz;
         if ((rc = gemm_f16_run(ctx, P, Cout, CRS, col, MP, wB, ldw, bias, 1, on, P, out_dtype, epilogue, 1, 0, 0, 0)))
             return rc;
     }
+    return B200_OK;
+}
+
+int b200_conv2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW, int64_t KH,
+                    int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py, int64_t dx, int64_t dy,
+                    const void* x, const void* w, const void* bias, void* out, int out_dtype, int epilogue) {
+    return b200_conv2d_grouped_f16(ctx, W, H, Cin, N, KW, KH, Cout, sx, sy, px, py, dx, dy, 1, x, w, bias, out, out_dtype,
+                                   epilogue);
+}
+
+int b200_conv2d_grouped_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW, int64_t KH,
+                            int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py, int64_t dx, int64_t dy,
+                            int64_t groups, const void* x, const void* w, const void* bias, void* out, int out_dtype,
+                            int epilogue) {
+    B200_REQUIRE(ctx && x && w && out, B200_EINVAL, "conv2d: null argument");
+    B200_REQUIRE(W > 0 && H > 0 && Cin > 0 && N > 0 && KW > 0 && KH > 0 && Cout > 0 && sx > 0 && sy > 0 &&
+                     dx > 0 && dy > 0 && px >= 0 && py >= 0 && groups > 0,
+                 B200_EINVAL, "conv2d: bad geometry");
+    B200_REQUIRE(Cin % groups == 0 && Cout % groups == 0, B200_DECLINE_EXTENT, "conv2d: %lld groups do not divide the channels",
+                 (long long)groups);
+    B200_REQUIRE(out_dtype == B200_F16 || out_dtype == B200_F32, B200_DECLINE_ELTYPE, "conv2d: out dtype %d", out_dtype);
+    const int64_t OW = convsize(W, KW, sx, px, dx), OH = convsize(H, KH, sy, py, dy);
+    B200_REQUIRE(OW > 0 && OH > 0, B200_DECLINE_EXTENT, "conv2d: empty output");
+    B200_CUDA(cudaSetDevice(ctx->device));
+    const int64_t CG = Cin / groups, COG = Cout / groups, P = OW * OH;
+    const size_t osz = out_dtype == B200_F16 ? 2 : 4;
+    for (int64_t g = 0; g < groups; ++g) {
+        // group g: input channels [g CG, (g+1) CG), output channels [g COG, (g+1) COG), its own slice of the weight
+        int rc = conv2d_group(ctx, W, H, CG, N, KW, KH, COG, sx, sy, px, py, dx, dy, (const __half*)x + g * CG * W * H,
+                              W * H * Cin, (const __half*)w + g * COG * (KW * KH * CG),
+                              bias ? (const __half*)bias + g * COG : nullptr, (char*)out + (size_t)(g * COG * P) * osz,
+                              P * Cout, out_dtype, epilogue);
+        if (rc) return rc;
+    }
+    return B200_OK;
+}
+
+// ------------------------------------------------------------------ transposed convolution
+} // extern "C"
+
+namespace b200 {
+
+// convtranspose2d (conv.jl:147-190), the gather form: one thread per output element, fp32 fma chain from the
+// bias over (ci, ky, kx); an input reaches an output where the stride divides.  x (W,H,Cin,N),
+// w (KW,KH,Cout/groups,Cin), out (OW,OH,Cout,N).  Deterministic: no atomics.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+convtranspose2d_f16_kernel(OutT* __restrict__ out, const __half* __restrict__ x, const __half* __restrict__ w,
+                           const __half* __restrict__ bias, int Wd, int Hd, int Cin, int KW, int KH, int Cout, int sx,
+                           int sy, int px, int py, int dx, int dy, int OW, int OH, int groups, int64_t ntot) {
+    const int COG = Cout / groups, CG = Cin / groups;
+    for (int64_t lin = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; lin < ntot; lin += (int64_t)gridDim.x * blockDim.x) {
+        const int ox = (int)(lin % OW);
+        int64_t t = lin / OW;
+        const int oy = (int)(t % OH);
+        t /= OH;
+        const int co = (int)(t % Cout);
+        const int64_t n = t / Cout;
+        float acc = bias ? __half2float(bias[co]) : 0.f;
+        const int cog = co % COG, g = co / COG;
+        const int bx = ox + px, by = oy + py;
+        for (int ci = g * CG; ci < (g + 1) * CG; ++ci)
+            for (int ky = 0; ky < KH; ++ky) {
+                const int ty = by - ky * dy;
+                if (ty < 0 || ty % sy != 0) continue;
+                const int iy = ty / sy;
+                if (iy >= Hd) continue;
+                for (int kx = 0; kx < KW; ++kx) {
+                    const int tx = bx - kx * dx;
+                    if (tx < 0 || tx % sx != 0) continue;
+                    const int ix = tx / sx;
+                    if (ix >= Wd) continue;
+                    acc = fmaf(__half2float(x[ix + (int64_t)Wd * (iy + (int64_t)Hd * (ci + (int64_t)Cin * n))]),
+                               __half2float(w[kx + KW * (ky + KH * (cog + (int64_t)COG * ci))]), acc);
+                }
+            }
+        if constexpr (sizeof(OutT) == 2) out[lin] = __float2half_rn(acc);
+        else out[lin] = acc;
+    }
+}
+
+// shuffleout (conv.jl:232-246): scatter the GEMM's (W*H, SX*SY*Cout) result into (SX*W, SY*H, Cout), adding the
+// bias in the output type.  Consecutive threads write consecutive addresses.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+shuffleout_kernel(OutT* __restrict__ out, const OutT* __restrict__ P, const __half* __restrict__ bias, int Wd, int Hd, int SX,
+                  int SY, int Cout, int64_t ntot) {
+    const int OW = Wd * SX, OH = Hd * SY;
+    for (int64_t lin = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; lin < ntot; lin += (int64_t)gridDim.x * blockDim.x) {
+        const int ox = (int)(lin % OW);
+        int64_t t = lin / OW;
+        const int oy = (int)(t % OH);
+        const int co = (int)(t / OH);
+        const int i = ox / SX, ddx = ox - i * SX, j = oy / SY, ddy = oy - j * SY;
+        const OutT v = P[(i + (int64_t)j * Wd) + (int64_t)Wd * Hd * (ddx + SX * (ddy + SY * co))];
+        if constexpr (sizeof(OutT) == 2)
+            out[lin] = bias ? __float2half_rn(__half2float(v) + __half2float(bias[co])) : v;
+        else
+            out[lin] = bias ? v + __half2float(bias[co]) : v;
+    }
+}
+
+static int64_t convtransposesize(int64_t n, int64_t k, int64_t s, int64_t p, int64_t d, int64_t op) {
+    return (n - 1) * s - 2 * p + d * (k - 1) + op + 1;
+}
+
+} // namespace b200
+
+extern "C" {
+
+int b200_convtranspose2d_f16(b200_ctx* ctx, int64_t W, int64_t H, int64_t Cin, int64_t N, int64_t KW, int64_t KH,
+                             int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py, int64_t dx, int64_t dy,
+                             int64_t opx, int64_t opy, int64_t groups, const void* x, const void* w, const void* bias,
+                             void* out, int out_dtype) {
+    B200_REQUIRE(ctx && x && w && out, B200_EINVAL, "convtranspose2d: null argument");
+    B200_REQUIRE(W > 0 && H > 0 && Cin > 0 && N > 0 && KW > 0 && KH > 0 && Cout > 0 && sx > 0 && sy > 0 && dx > 0 &&
+                     dy > 0 && px >= 0 && py >= 0 && opx >= 0 && opy >= 0 && groups > 0,
+                 B200_EINVAL, "convtranspose2d: bad geometry");
+    B200_REQUIRE(Cin % groups == 0 && Cout % groups == 0, B200_DECLINE_EXTENT,
+                 "convtranspose2d: %lld groups do not divide the channels", (long long)groups);
+    B200_REQUIRE(out_dtype == B200_F16 || out_dtype == B200_F32, B200_DECLINE_ELTYPE, "convtranspose2d: out dtype %d",
+                 out_dtype);
+    const int64_t OW = convtransposesize(W, KW, sx, px, dx, opx), OH = convtransposesize(H, KH, sy, py, dy, opy);
+    B200_REQUIRE(OW > 0 && OH > 0, B200_DECLINE_EXTENT, "convtranspose2d: empty output");
+    B200_REQUIRE(OW < (1ll << 31) && OH < (1ll << 31) && W * H * Cin < (1ll << 31), B200_DECLINE_EXTENT,
+                 "convtranspose2d: extent beyond int32");
+    B200_CUDA(cudaSetDevice(ctx->device));
+    const size_t osz = out_dtype == B200_F16 ? 2 : 4;
+    // shufflecase (conv.jl:219-222): stride equal to the kernel, no padding, dilation or output padding, one group —
+    // every output pixel is fed by exactly one input pixel and one weight slice, i.e. a GEMM over
+    // (W*H) x Cin x (KW*KH*Cout) and a depth-to-space interleave.
+    const bool shuffle = groups == 1 && dx == 1 && dy == 1 && px == 0 && py == 0 && opx == 0 && opy == 0 && KW == sx &&
+                         KH == sy;
+    if (shuffle) {
+        int rc;
+        const int64_t NC = KW * KH * Cout, P = W * H;
+        void *wm = nullptr, *pbuf = nullptr;
+        if ((rc = ws_scratch(ctx, (size_t)(Cin * NC) * 2, &wm))) return rc;
+        if ((rc = ws_scratch(ctx, (size_t)(P * NC) * osz, &pbuf))) return rc;
+        // (kx, ky, co, ci) -> (ci, kx, ky, co): the GEMM's B operand with Cin contiguous (a permute of a weight: load-time
+        // work in a planned graph, done per call here as the reference does)
+        const int64_t shape[4] = {Cin, KW, KH, Cout};
+        const int64_t stride[4] = {KW * KH * Cout, 1, KW, KW * KH};
+        if ((rc = b200_permute4(ctx, w, wm, shape, stride, 2))) return rc;
+        for (int64_t n = 0; n < N; ++n) {
+            const __half* xn = (const __half*)x + n * P * Cin;   // (P, Cin), pixels contiguous
+            if ((rc = gemm_f16_run(ctx, P, NC, Cin, xn, P, wm, Cin, nullptr, 0, pbuf, P, out_dtype, B200_EPI_NONE, 1, 0, 0, 0)))
+                return rc;
+            const int64_t ntot = OW * OH * Cout;
+            void* on = (char*)out + (size_t)(n * ntot) * osz;
+            if (out_dtype == B200_F16)
+                shuffleout_kernel<__half><<<grid_for(ctx, ntot), 256, 0, ctx->stream>>>((__half*)on, (const __half*)pbuf,
+                                                                                          (const __half*)bias, (int)W, (int)H,
+                                                                                          (int)sx, (int)sy, (int)Cout, ntot);
+            else
+                shuffleout_kernel<float><<<grid_for(ctx, ntot), 256, 0, ctx->stream>>>((float*)on, (const float*)pbuf,
+                                                                                        (const __half*)bias, (int)W, (int)H,
+                                                                                        (int)sx, (int)sy, (int)Cout, ntot);
+            ctx->launches++;
+            B200_CUDA(cudaGetLastError());
+        }
+        return B200_OK;
+    }
+    const int64_t ntot = OW * OH * Cout * N;
+    if (out_dtype == B200_F16)
+        convtranspose2d_f16_kernel<__half><<<grid_for(ctx, ntot), 256, 0, ctx->stream>>>(
+            (__half*)out, (const __half*)x, (const __half*)w, (const __half*)bias, (int)W, (int)H, (int)Cin, (int)KW, (int)KH,
+            (int)Cout, (int)sx, (int)sy, (int)px, (int)py, (int)dx, (int)dy, (int)OW, (int)OH, (int)groups, ntot);
+    else
+        convtranspose2d_f16_kernel<float><<<grid_for(ctx, ntot), 256, 0, ctx->stream>>>(
+            (float*)out, (const __half*)x, (const __half*)w, (const __half*)bias, (int)W, (int)H, (int)Cin, (int)KW, (int)KH,
+            (int)Cout, (int)sx, (int)sy, (int)px, (int)py, (int)dx, (int)dy, (int)OW, (int)OH, (int)groups, ntot);
+    ctx->launches++;
+    B200_CUDA(cudaGetLastError());
     return B200_OK;
 }
 

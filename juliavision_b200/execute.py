@@ -23,7 +23,7 @@ import numpy as np
 from ._lib import B200Error
 from .attention import sdpa
 from .context import Ctx, DeviceArray
-from .conv import convolution_, convsize
+from .conv import convolution_, convolutiontranspose_, convsize, convtransposesize
 from .elementwise import act_, add_, clamp_, maxpool2d_, to_copy_
 from .graph import Buffer, Graph, Op, evalshape
 from .layernorm import layernorm_
@@ -452,18 +452,29 @@ def _op_maxpool(run: _Run, op: Op):
 
 
 def _op_convolution(run: _Run, op: Op):
-    x, w = run.value(op.ins[0]), run.value(op.ins[1])       # ops.jl:1114-1222 (2-D, one group)
+    x, w = run.value(op.ins[0]), run.value(op.ins[1])       # ops.jl:1114-1222 (2-D)
     bias = run.value(op.ins[2]) if len(op.ins) >= 3 else None
     rev = lambda v: tuple(int(t) for t in reversed(v))      # torch (h, w) -> (x, y)
     stride, padding, dilation = rev(op.attrs["arg3"]), rev(op.attrs["arg4"]), rev(op.attrs["arg5"])
-    if bool(op.attrs.get("arg6", False)) or int(op.attrs.get("arg8", 1)) != 1 or x.ndim != 4:
-        raise B200Error(17, "convolution: only plain 2-D convolutions with one group are lowered to the GEMM")
+    groups = int(op.attrs.get("arg8", 1))
+    if x.ndim != 4:
+        raise B200Error(17, "convolution: only 2-D convolutions (callers lift 1-D ones, as the reference does)")
+    if bool(op.attrs.get("arg6", False)):                    # transposed: arg7 is output_padding
+        outpad = rev(op.attrs.get("arg7", (0, 0)))
+        W, H, _, N = x.shape
+        KW, KH, COG, _ = w.shape
+        OW = convtransposesize(W, KW, stride[0], padding[0], dilation[0], outpad[0])
+        OH = convtransposesize(H, KH, stride[1], padding[1], dilation[1], outpad[1])
+        out = run.alloc(op.out, OW, OH, COG * groups, N)
+        convolutiontranspose_(run.ctx, out, run.contiguous(op.ins[0] + "#c", x), w, bias, stride, padding, dilation,
+                              outpad, groups)
+        return out
     W, H, _, N = x.shape
     KW, KH, _, Cout = w.shape
     OW = convsize(W, KW, stride[0], padding[0], dilation[0])
     OH = convsize(H, KH, stride[1], padding[1], dilation[1])
     out = run.alloc(op.out, OW, OH, Cout, N)
-    convolution_(run.ctx, out, run.contiguous(op.ins[0] + "#c", x), w, bias, stride, padding, dilation, 1,
+    convolution_(run.ctx, out, run.contiguous(op.ins[0] + "#c", x), w, bias, stride, padding, dilation, groups,
                  act=_act_name(op.attrs))
     return out
 

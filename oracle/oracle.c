@@ -399,6 +399,90 @@ void ora_conv2d_f16(int64_t W, int64_t Hh, int64_t Cin, int64_t Nn, int64_t KW, 
 }
 
 /*
+ * conv.jl:26-51 (conv2d) with GROUPS >= 1: w is (KW,KH,Cin/groups,Cout); output channel co reads the input
+ * channels of its own group, g = co / (Cout/groups).
+ */
+void ora_conv2d_grouped_f16(int64_t W, int64_t Hh, int64_t Cin, int64_t Nn, int64_t KW, int64_t KH,
+                            int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py,
+                            int64_t dx, int64_t dy, int64_t groups, const f16bits* x, const f16bits* w,
+                            const f16bits* bias, void* out, int out_dtype, int epi) {
+    int64_t OW = ora_convsize(W, KW, sx, px, dx), OH = ora_convsize(Hh, KH, sy, py, dy);
+    int64_t CG = Cin / groups, COG = Cout / groups;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int64_t n = 0; n < Nn; ++n)
+        for (int64_t co = 0; co < Cout; ++co)
+            for (int64_t oy = 0; oy < OH; ++oy)
+                for (int64_t ox = 0; ox < OW; ++ox) {
+                    float acc = bias ? h2f(bias[co]) : 0.0f;
+                    int64_t g = co / COG;
+                    int64_t bx = ox * sx - px, by = oy * sy - py;
+                    for (int64_t ci = 0; ci < CG; ++ci) {
+                        int64_t xc = g * CG + ci;
+                        for (int64_t ky = 0; ky < KH; ++ky) {
+                            int64_t iy = by + ky * dy;
+                            if (iy < 0 || iy >= Hh) continue;
+                            for (int64_t kx = 0; kx < KW; ++kx) {
+                                int64_t ix = bx + kx * dx;
+                                if (ix < 0 || ix >= W) continue;
+                                acc = fmaf(h2f(x[ix + W * (iy + Hh * (xc + Cin * n))]),
+                                           h2f(w[kx + KW * (ky + KH * (ci + CG * co))]), acc);
+                            }
+                        }
+                    }
+                    int64_t o = ox + OW * (oy + OH * (co + Cout * n));
+                    if (out_dtype == ORA_F16)
+                        ((f16bits*)out)[o] = f2h(apply_epi(epi, h2f(f2h(acc))));
+                    else
+                        ((float*)out)[o] = apply_epi(epi, acc);
+                }
+}
+
+/* conv.jl:194 (convtransposesize) */
+int64_t ora_convtransposesize(int64_t n, int64_t k, int64_t s, int64_t p, int64_t d, int64_t op) {
+    return (n - 1) * s - 2 * p + d * (k - 1) + op + 1;
+}
+
+/*
+ * conv.jl:147-190 (convtranspose2d), the gather form: x (W,H,Cin,N), w (KW,KH,Cout/groups,Cin) — the transposed
+ * weight has its two channel axes the other way round — out (OW,OH,Cout,N); fp32 fma chain from the bias over
+ * (ci, ky, kx) ascending; an input reaches an output where the stride divides.
+ */
+void ora_convtranspose2d_f16(int64_t W, int64_t Hh, int64_t Cin, int64_t Nn, int64_t KW, int64_t KH,
+                             int64_t Cout, int64_t sx, int64_t sy, int64_t px, int64_t py, int64_t dx,
+                             int64_t dy, int64_t opx, int64_t opy, int64_t groups, const f16bits* x,
+                             const f16bits* w, const f16bits* bias, void* out, int out_dtype) {
+    int64_t OW = ora_convtransposesize(W, KW, sx, px, dx, opx), OH = ora_convtransposesize(Hh, KH, sy, py, dy, opy);
+    int64_t COG = Cout / groups, CG = Cin / groups;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int64_t n = 0; n < Nn; ++n)
+        for (int64_t co = 0; co < Cout; ++co)
+            for (int64_t oy = 0; oy < OH; ++oy)
+                for (int64_t ox = 0; ox < OW; ++ox) {
+                    float acc = bias ? h2f(bias[co]) : 0.0f;
+                    int64_t cog = co % COG, g = co / COG;
+                    int64_t bx = ox + px, by = oy + py;
+                    for (int64_t ci = g * CG; ci < (g + 1) * CG; ++ci)
+                        for (int64_t ky = 0; ky < KH; ++ky) {
+                            int64_t ty = by - ky * dy;
+                            if (ty < 0 || ty % sy != 0) continue;
+                            int64_t iy = ty / sy;
+                            if (iy >= Hh) continue;
+                            for (int64_t kx = 0; kx < KW; ++kx) {
+                                int64_t tx = bx - kx * dx;
+                                if (tx < 0 || tx % sx != 0) continue;
+                                int64_t ix = tx / sx;
+                                if (ix >= W) continue;
+                                acc = fmaf(h2f(x[ix + W * (iy + Hh * (ci + Cin * n))]),
+                                           h2f(w[kx + KW * (ky + KH * (cog + COG * ci))]), acc);
+                            }
+                        }
+                    int64_t o = ox + OW * (oy + OH * (co + Cout * n));
+                    if (out_dtype == ORA_F16) ((f16bits*)out)[o] = f2h(acc);
+                    else ((float*)out)[o] = acc;
+                }
+}
+
+/*
  * conv_coopmat.jl:246-289 (im2col_kernel!): col is (MP, CRSP) column-major,
  * row m = pixel (ow + OW*(oh + OH*n)), column crs = kw + KW*(kh + KH*cin);
  * rows >= NPQ, columns >= CRS and taps outside the image are zero.

@@ -219,6 +219,43 @@ def conv2d(x, w, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), epi=
     return out
 
 
+def conv2d_grouped(x, w, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, epi="none",
+                   out_dtype=np.float16):
+    """x: torch (N,Cin,H,W); w: torch (Cout,Cin/groups,KH,KW)."""
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    w = np.ascontiguousarray(w, dtype=np.float16)
+    N, Cin, H, W = x.shape
+    Cout, _, KH, KW = w.shape
+    (sy, sx), (py, px), (dy, dx) = stride, padding, dilation
+    OW, OH = convsize(W, KW, sx, px, dx), convsize(H, KH, sy, py, dy)
+    out = np.empty((N, Cout, OH, OW), dtype=out_dtype)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float16)
+    lib().ora_conv2d_grouped_f16(*_i64(W, H, Cin, N, KW, KH, Cout, sx, sy, px, py, dx, dy, groups), _p(x), _p(w),
+                                 _p(b), _p(out), C.c_int(_dt(out_dtype)), C.c_int(EPI[epi]))
+    return out
+
+
+def convtransposesize(n, k, s, p, d, op):
+    return (n - 1) * s - 2 * p + d * (k - 1) + op + 1
+
+
+def convtranspose2d(x, w, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), output_padding=(0, 0), groups=1,
+                    out_dtype=np.float16):
+    """x: torch (N,Cin,H,W); w: torch (Cin,Cout/groups,KH,KW); stride etc. in torch (h,w) order."""
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    w = np.ascontiguousarray(w, dtype=np.float16)
+    N, Cin, H, W = x.shape
+    _, COG, KH, KW = w.shape
+    Cout = COG * groups
+    (sy, sx), (py, px), (dy, dx), (opy, opx) = stride, padding, dilation, output_padding
+    OW, OH = convtransposesize(W, KW, sx, px, dx, opx), convtransposesize(H, KH, sy, py, dy, opy)
+    out = np.empty((N, Cout, OH, OW), dtype=out_dtype)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float16)
+    lib().ora_convtranspose2d_f16(*_i64(W, H, Cin, N, KW, KH, Cout, sx, sy, px, py, dx, dy, opx, opy, groups), _p(x),
+                                  _p(w), _p(b), _p(out), C.c_int(_dt(out_dtype)))
+    return out
+
+
 def im2col(x, KH, KW, stride, padding, dilation, MP, CRSP):
     """Returns col as a torch-order (CRSP, MP) array (= reference column-major (MP,CRSP))."""
     x = np.ascontiguousarray(x, dtype=np.float16)

@@ -143,3 +143,61 @@ def test_pool_and_workspace(ctx):
     assert reserved() == before                                                # nothing new is taken from the driver
     with pytest.raises(jv.B200Error):
         _lib.check(_lib.lib().b200_pool_free(ctx.handle, C.c_void_p(12345)))
+
+
+# (N, Cin, H, W, Cout, KH, KW, stride, padding, dilation, groups) in torch order
+GROUPED = [(2, 16, 20, 24, 32, 3, 3, (1, 1), (1, 1), (1, 1), 2),     # aligned slices: tensor-core GEMM per group
+           (1, 6, 9, 8, 8, 3, 3, (2, 1), (1, 1), (1, 1), 2),         # unaligned slices: the scalar GEMM
+           (2, 8, 12, 12, 8, 3, 3, (1, 1), (1, 1), (1, 1), 8),       # depthwise
+           (1, 32, 16, 16, 64, 1, 1, (1, 1), (0, 0), (1, 1), 4)]     # grouped 1x1: no gather
+
+
+@pytest.mark.parametrize("N,Cin,H,W,Cout,KH,KW,stride,padding,dilation,groups", GROUPED)
+def test_grouped_conv_vs_oracle(ctx, ora, N, Cin, H, W, Cout, KH, KW, stride, padding, dilation, groups):
+    """conv2d with GROUPS > 1 (conv.jl:26-51): every group lowered like the ungrouped convolution."""
+    rng = np.random.default_rng(Cin * 13 + groups)
+    x = np.float16(rng.standard_normal((N, Cin, H, W)) * 0.5)
+    w = np.float16(rng.standard_normal((Cout, Cin // groups, KH, KW)) * 0.2)
+    b = np.float16(rng.standard_normal(Cout) * 0.2)
+    ref = ora.conv2d_grouped(x, w, b, stride, padding, dilation, groups, epi="relu")
+    out = ctx.allocate(np.float16, ref.shape[3], ref.shape[2], Cout, N)
+    ctx.fill_bytes(out, 0xFF)
+    ctx.ws.reset()
+    jv.convolution_(ctx, out, ctx.toback(x), ctx.toback(w), ctx.toback(b), stride[::-1], padding[::-1], dilation[::-1],
+                    groups, act="relu")
+    ctx.synchronize()
+    got = out.to_host()
+    assert np.all(np.isfinite(got))
+    assert relerr(got, ref) < 5e-3, describe(got, ref, 5e-3)
+
+
+# (N, Cin, H, W, Cout, KH, KW, stride, padding, dilation, output_padding, groups)
+TRANSPOSED = [(1, 64, 16, 16, 32, 2, 2, (2, 2), (0, 0), (1, 1), (0, 0), 1),      # SAM 2's upsampler: shufflecase -> GEMM
+              (2, 24, 9, 7, 16, 2, 3, (2, 3), (0, 0), (1, 1), (0, 0), 1),        # shufflecase, odd extents, two images
+              (2, 4, 5, 6, 6, 3, 2, (2, 3), (1, 0), (1, 2), (1, 1), 2),          # grouped, padded, dilated, output padding
+              (1, 8, 10, 10, 8, 3, 3, (1, 1), (1, 1), (1, 1), (0, 0), 8),        # depthwise (Kokoro's upsampler form)
+              (1, 16, 8, 8, 8, 4, 4, (2, 2), (1, 1), (1, 1), (0, 0), 1)]         # overlapping receptive fields: the gather
+
+
+@pytest.mark.parametrize("N,Cin,H,W,Cout,KH,KW,stride,padding,dilation,outpad,groups", TRANSPOSED)
+def test_transposed_conv_vs_oracle(ctx, ora, N, Cin, H, W, Cout, KH, KW, stride, padding, dilation, outpad, groups):
+    """convolutiontranspose! (conv.jl:247-290): the GEMM + shuffle route where the receptive fields tile the output,
+    the deterministic gather elsewhere; both against the oracle's gather (conv.jl:147-190)."""
+    rng = np.random.default_rng(Cin * 7 + Cout)
+    x = np.float16(rng.standard_normal((N, Cin, H, W)) * 0.5)
+    w = np.float16(rng.standard_normal((Cin, Cout // groups, KH, KW)) * 0.2)
+    b = np.float16(rng.standard_normal(Cout) * 0.2)
+    for out_dtype in (np.float16, np.float32):
+        ref = ora.convtranspose2d(x, w, b, stride, padding, dilation, outpad, groups, out_dtype=np.float32)
+        out = ctx.allocate(out_dtype, ref.shape[3], ref.shape[2], Cout, N)
+        ctx.fill_bytes(out, 0xFF)
+        ctx.ws.reset()
+        dw = ctx.toback(w)
+        assert jv.shufflecase(dw, stride[::-1], padding[::-1], dilation[::-1], outpad[::-1], groups) == \
+            (groups == 1 and (KH, KW) == stride and padding == (0, 0) and outpad == (0, 0) and dilation == (1, 1))
+        jv.convolutiontranspose_(ctx, out, ctx.toback(x), dw, ctx.toback(b), stride[::-1], padding[::-1], dilation[::-1],
+                                 outpad[::-1], groups)
+        ctx.synchronize()
+        got = out.to_host()
+        assert got.shape == ref.shape and np.all(np.isfinite(got))
+        assert relerr(got, ref) < 5e-3, describe(got, ref, 5e-3)
