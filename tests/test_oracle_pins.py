@@ -250,3 +250,52 @@ def test_hiera_reference_window_round_trip():
     assert xw.shape == (8, 16, 3)
     assert np.array_equal(xw[1, 0], x[0, 0, 4])          # second window of the first row starts at column 4
     assert np.array_equal(_unpartition(xw, 4, 2, 8), x)
+
+
+def test_grouped_conv_is_the_ungrouped_one_per_group(ora):
+    """conv2d with GROUPS (conv.jl:26-51): output channel co reads its own group's inputs — so a grouped convolution
+    equals the ungrouped one applied to each group's channel slices, bit for bit (same fma chain)."""
+    rng = np.random.default_rng(0)
+    x = np.float16(rng.standard_normal((2, 6, 9, 8)))
+    w = np.float16(rng.standard_normal((8, 3, 3, 3)) * 0.3)
+    b = np.float16(rng.standard_normal(8))
+    got = ora.conv2d_grouped(x, w, b, (2, 1), (1, 1), (1, 1), groups=2, out_dtype=np.float32)
+    ref = np.concatenate([ora.conv2d(x[:, :3], w[:4], b[:4], (2, 1), (1, 1), (1, 1), out_dtype=np.float32),
+                          ora.conv2d(x[:, 3:], w[4:], b[4:], (2, 1), (1, 1), (1, 1), out_dtype=np.float32)], 1)
+    assert np.array_equal(got, ref)
+
+
+def _convtranspose_scatter(x, w, b, s, p, d, op, groups):
+    """The scatter reading of a transposed convolution ("each input paints a kernel-sized patch") in float64: an
+    independent statement of what the oracle's gather (conv.jl:147-190) must equal."""
+    N, Cin, H, W = x.shape
+    _, COG, KH, KW = w.shape
+    OH = (H - 1) * s[0] - 2 * p[0] + d[0] * (KH - 1) + op[0] + 1
+    OW = (W - 1) * s[1] - 2 * p[1] + d[1] * (KW - 1) + op[1] + 1
+    out = np.zeros((N, COG * groups, OH, OW))
+    CG = Cin // groups
+    for n in range(N):
+        for ci in range(Cin):
+            g = ci // CG
+            for iy in range(H):
+                for ix in range(W):
+                    for ky in range(KH):
+                        for kx in range(KW):
+                            oy, ox = iy * s[0] - p[0] + ky * d[0], ix * s[1] - p[1] + kx * d[1]
+                            if 0 <= oy < OH and 0 <= ox < OW:
+                                out[n, g * COG:(g + 1) * COG, oy, ox] += float(x[n, ci, iy, ix]) * w[ci, :, ky, kx].astype(np.float64)
+    return out + b.astype(np.float64)[None, :, None, None]
+
+
+def test_transposed_conv_gather_equals_the_scatter(ora):
+    rng = np.random.default_rng(1)
+    x = np.float16(rng.standard_normal((2, 4, 5, 6)))
+    b = np.float16(rng.standard_normal(6))
+    for s, p, d, op, groups in (((2, 2), (0, 0), (1, 1), (0, 0), 1), ((2, 3), (1, 0), (1, 2), (1, 1), 2),
+                                ((1, 1), (1, 1), (1, 1), (0, 0), 1)):
+        w = np.float16(rng.standard_normal((4, 6 // groups, 3, 2)) * 0.3)
+        got = ora.convtranspose2d(x, w, b, s, p, d, op, groups, out_dtype=np.float32)
+        ref = _convtranspose_scatter(x, w, b, s, p, d, op, groups)
+        assert got.shape == ref.shape
+        assert np.max(np.abs(got - ref)) < 1e-5
+        assert ora.convtransposesize(5, 3, s[0], p[0], d[0], op[0]) == ref.shape[2]      # conv.jl:194
