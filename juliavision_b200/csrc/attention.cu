@@ -31,15 +31,19 @@ constexpr int ATT_TILE_BYTES = 128 * 128; // one swizzle atom of an operand tile
 #endif
 // Two shapes of CTA, chosen by the head dimension:
 //   EP = 64  (E <= 64):        two query tiles of 128 per CTA, K/V rings of 4 stages x 16 KB
-//   EP = 128 (64 < E <= 128):  one query tile of 128 per CTA; every operand tile is two swizzle atoms along E
-//                              (columns 0-63, 64-127, the second zero-filled past E by the tensor map), S = Q K'
-//                              runs over both, O has 128 columns; K/V rings of 3 stages x 32 KB
+//   EP = 128 (64 < E <= 128):  two query tiles of 128 per CTA as well; every operand tile is two swizzle atoms along
+//                              E (columns 0-63, 64-127, the second zero-filled past E by the tensor map), S = Q K'
+//                              runs over both, O has 128 columns per tile — S 2 x 128 + O 2 x 128 fill the tensor
+//                              memory, so P is written over the first 64 columns of its tile's S once the softmax
+//                              has pulled S into registers, and a tile's Q K'(j+1) is issued after its P V(j)
+//                              (the two tiles' chains interleave on the tensor core); K/V rings of 2 stages x 32 KB
 // The reference's own fused tiling is E = 72 padded to 80 (flash.jl:1149-1157, flashepad kernelplans.jl).
 template <int EP> struct AttCfg {
     static_assert(EP == 64 || EP == 128, "head dim is padded to one or two swizzle atoms");
     static constexpr int ATOMS = EP / 64;              // 16 KB atoms per operand tile
-    static constexpr int NT = EP == 64 ? 2 : 1;        // query tiles per CTA
-    static constexpr int KV_STAGES = EP == 64 ? 4 : 3;
+    static constexpr int NT = 2;                       // query tiles per CTA
+    static constexpr int KV_STAGES = EP == 64 ? 4 : 2;
+    static constexpr bool P_IN_S = EP == 128;          // P shares its tile's S columns (tensor memory is full otherwise)
     static constexpr int OP_BYTES = ATOMS * ATT_TILE_BYTES;   // one Q, K or V tile
     // shared-memory map, in 16 KB atoms
     static constexpr int T_Q = 0;                              // NT tiles
@@ -50,7 +54,8 @@ template <int EP> struct AttCfg {
     static_assert(SMEM_BYTES <= 232448, "shared memory over budget");
 };
 // tensor-memory map (512 columns): S of tile t, fp32, at [128 t, 128 t + 128); O of tile t, fp32, at
-// [256 + EP t, ... + EP); P of tile t, fp16 packed two keys per column, at [384 + 64 t, ... + 64)
+// [256 + EP t, ... + EP); P of tile t, fp16 packed two keys per column, at [384 + 64 t, ... + 64) for EP = 64 and
+// over the first 64 columns of S_t for EP = 128
 constexpr int ATT_TMEM_COLS = 512;
 constexpr int ATT_S_COL = 0;
 constexpr int ATT_O_COL = 256;
@@ -280,13 +285,16 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
             const uint32_t q_addr = smem_u32(tile_ptr(Cfg::T_Q + t * Cfg::ATOMS));
             const uint32_t s_tmem = tmem_base + ATT_S_COL + t * 128;
             const uint32_t o_tmem = tmem_base + ATT_O_COL + t * EP;
-            const uint32_t p_tmem = tmem_base + ATT_P_COL + t * 64;
+            const uint32_t p_tmem = Cfg::P_IN_S ? s_tmem : tmem_base + ATT_P_COL + t * 64;
 
             auto issue_qk = [&](int j) -> bool {
                 const int sk = j % ATT_KV_STAGES;
                 if (!mbar_wait(&k_full[sk], (uint32_t)((j / ATT_KV_STAGES) & 1), p.d_status, KST_WAIT_FULL, abort_flag))
                     return false;
-                if (j > 0 && !mbar_wait(&s_empty[t], (uint32_t)((j - 1) & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag))
+                // With P in S's columns this product is issued after P V(j-1), which read P after the softmax had taken
+                // S(j-1), and UMMAs of one thread run in issue order: nothing else to wait for.
+                if (!Cfg::P_IN_S && j > 0 &&
+                    !mbar_wait(&s_empty[t], (uint32_t)((j - 1) & 1), p.d_status, KST_WAIT_SOFTMAX, abort_flag))
                     return false;
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(tile_ptr(Cfg::T_K + sk * Cfg::ATOMS));
@@ -305,7 +313,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
             bool ok = mbar_wait(&q_full[t], 0, p.d_status, KST_WAIT_FULL, abort_flag);
             if (ok && nblk > 0) ok = issue_qk(0);
             for (int j = 0; ok && j < nblk; ++j) {
-                if (j + 1 < nblk && !issue_qk(j + 1)) break;
+                if (!Cfg::P_IN_S && j + 1 < nblk && !issue_qk(j + 1)) break;
                 const int sv = j % ATT_KV_STAGES;
                 if (!mbar_wait(&v_full[sv], (uint32_t)((j / ATT_KV_STAGES) & 1), p.d_status, KST_WAIT_FULL, abort_flag)) break;
                 if (j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 7);   // issuer reaches its wait for P(j)
@@ -321,6 +329,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
                 umma_commit(&pv_done[t]);
                 umma_commit(&v_empty[sv]);   // one of `ntiles` arrivals that free this V stage
                 if (j < 6) ATT_TRACE(64 * t + 8 + 8 * j + 1);   // P V(j) issued
+                if (Cfg::P_IN_S && j + 1 < nblk && !issue_qk(j + 1)) break;   // overwrites P(j): after the product that reads it
             }
         }
     } else {
@@ -333,7 +342,7 @@ attention_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapQ,
             const uint32_t lane_base = uint32_t(quad * 32) << 16;
             const uint32_t s_tmem = tmem_base + lane_base + ATT_S_COL + t * 128;
             const uint32_t o_tmem = tmem_base + lane_base + ATT_O_COL + t * EP;
-            const uint32_t p_tmem = tmem_base + lane_base + ATT_P_COL + t * 64;
+            const uint32_t p_tmem = Cfg::P_IN_S ? s_tmem : tmem_base + lane_base + ATT_P_COL + t * 64;
             const float sc = p.scale_log2;
             const float sce = BIAS ? 1.0f : sc;   // with a bias the scores are rescaled when it is added
             float m_run = -INFINITY, l_run = 0.f;
@@ -931,7 +940,7 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
     p.bias = bptr;
     p.bsK = bs[0]; p.bsQ = bs[1]; p.bsH = bs[2]; p.bsB = bs[3];
     p.bias_vec = bptr && bs[0] == 1 && al16(bptr) && bs[1] % 8 == 0 && bs[2] % 8 == 0 && bs[3] % 8 == 0;
-    const bool wide = E > 64;                              // two swizzle atoms along E, one query tile per CTA
+    const bool wide = E > 64;                              // two swizzle atoms along E
     const int64_t item_rows = wide ? AttCfg<128>::NT * ATT_BR : AttCfg<64>::NT * ATT_BR;
     const size_t smem_bytes = wide ? AttCfg<128>::SMEM_BYTES : AttCfg<64>::SMEM_BYTES;
     auto launch = [&](dim3 grid) -> cudaError_t {
@@ -989,7 +998,7 @@ int b200_attention_f16_bias(b200_ctx* ctx, int64_t E, int64_t Lq, int64_t Lk, in
     }
     // Split the pairs of a last wave that would leave more than half of the SMs idle — but not a
     // pair whose second tile does not exist.
-    int64_t nsplit = (!wide && pairs > sms && rem > 0 && 2 * rem <= sms && Lq % (2 * ATT_BR) == 0) ? rem : 0;
+    int64_t nsplit = (pairs > sms && rem > 0 && 2 * rem <= sms && Lq % (2 * ATT_BR) == 0) ? rem : 0;
     p.pair_ctas = (int)(pairs - nsplit);
     B200_CUDA(launch(dim3((unsigned)(pairs + nsplit), 1, 1)));
     ctx->launches++;
