@@ -58,6 +58,8 @@ template <int BN, typename OutT, int NCTA> struct GemmCfg {
     static_assert(SMEM_BYTES <= SMEM_LIMIT, "shared memory over budget");
     static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
     static_assert(B_COLS % 64 == 0, "each CTA stages whole 64-column slabs of B");
+    static_assert((EPI_WARPS * (BN / (EPI_WARPS / 4)) * 4) % 512 == 0 && (STAGES * STAGE_BYTES) % 1024 == 0,
+                  "the epilogue slabs must start on the swizzle pattern's period");
 };
 
 template <typename OutT> struct GemmParams {
@@ -418,6 +420,10 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             const uint32_t tacc = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
             const int act_kind = p.epilogue;
             uint8_t* rowp = wstg + lane * RB;
+            // The slab's rows are 32 B (fp16) or 64 B (fp32) apart, so lanes four (two) apart would hit the same
+            // banks.  The store map swizzles at that width (16-byte chunk index ^= address bits from 7 up), which
+            // spreads a warp's 16-byte stores over all banks: four wavefronts per instruction instead of eight.
+            const int swz = RB == 32 ? ((lane >> 2) & 1) : ((lane >> 1) & 3);
 
 #pragma unroll 1
             for (int c = 0; c < NCH; ++c) {
@@ -487,7 +493,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                             h[1] = act(__floats2half2_rn(v[j * 8 + 2] + b0.z, v[j * 8 + 3] + b0.w));
                             h[2] = act(__floats2half2_rn(v[j * 8 + 4] + b1.x, v[j * 8 + 5] + b1.y));
                             h[3] = act(__floats2half2_rn(v[j * 8 + 6] + b1.z, v[j * 8 + 7] + b1.w));
-                            *reinterpret_cast<uint4*>(rowp + (j << 4)) = o;
+                            *reinterpret_cast<uint4*>(rowp + ((j ^ swz) << 4)) = o;
                         }
                     };
                     switch (act_kind) {
@@ -515,11 +521,11 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         o.y = apply_act(act_kind, v[j * 4 + 1] + b.y);
                         o.z = apply_act(act_kind, v[j * 4 + 2] + b.z);
                         o.w = apply_act(act_kind, v[j * 4 + 3] + b.w);
-                        *reinterpret_cast<float4*>(rowp + (j << 4)) = o;
+                        *reinterpret_cast<float4*>(rowp + ((j ^ swz) << 4)) = o;
                     }
                 }
-                // shared -> global by the bulk-store engine: one instruction for the 16 x 32 box (plain rows in the
-                // slab), clipped at the ragged edges of the output.
+                // shared -> global by the bulk-store engine: one instruction for the 16 x 32 box (the engine undoes
+                // the slab's swizzle), clipped at the ragged edges of the output.
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
@@ -683,7 +689,7 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
         uint64_t str[2] = {(uint64_t)ldo * osz, (uint64_t)(nbatch > 1 ? sO : ldo * N) * osz};
         uint32_t box[3] = {16, 32, 1};
         int rc = make_tmap(ctx, &tO, sizeof(OutT) == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, out,
-                           dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+                           dims, str, box, sizeof(OutT) == 2 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B);
         if (rc) return rc;
     }
     GemmParams<OutT> p;
