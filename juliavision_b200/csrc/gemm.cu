@@ -65,7 +65,7 @@ template <int BN, typename OutT, int NCTA> struct GemmCfg {
 template <typename OutT> struct GemmParams {
     int64_t M, N, K;       // out features, tokens, reduction
     int tiles_m, tiles_n;  // feature tiles, token tiles
-    int64_t total_tiles;   // tiles_m * tiles_n * nbatch
+    uint32_t total_tiles;  // tiles_m * tiles_n * nbatch (times num_kb below 2^31, checked at launch)
     int num_kb;
     OutT* out;             // out(M,N): element (i,j) of plane b at out[b*strideO + j*ldo + i]
     int64_t ldo, strideO;
@@ -99,28 +99,32 @@ template <typename OutT> struct GemmParams {
 //                    k-block (that segment comes last in the worker's range); the workers holding
 //                    its later k-blocks (their first segment) leave fp32 partials for it.
 struct SegIter {
-    int64_t tile, u, uend, step, total_tiles;
+    // 32-bit throughout (the host refuses a launch whose tiles x k-blocks do not fit): every role of every
+    // CTA walks this per tile, and what the sixteen epilogue warps issue there is taken from the UMMA
+    // issuer's share of the schedulers, so a 64-bit division here costs main-loop time.
+    uint32_t tile, u, uend, step;
     int kb0, kb1, nkb, streamk;
-    __device__ __forceinline__ static int64_t range_start(int64_t units, int64_t w, int64_t W) { return units * w / W; }
+    __device__ __forceinline__ static uint32_t range_start(uint32_t units, uint32_t w, uint32_t W) {
+        return units / W * w + units % W * w / W;   // floor(units * w / W) without leaving 32 bits (w <= W < 2^16)
+    }
     __device__ __forceinline__ void set() {
         if (streamk) {
-            tile = u / nkb;
-            kb0 = (int)(u - tile * nkb);
-            const int64_t left = uend - u;
-            kb1 = (int)((int64_t)(nkb - kb0) < left ? nkb : kb0 + left);
+            tile = u / (uint32_t)nkb;
+            kb0 = (int)(u - tile * (uint32_t)nkb);
+            const uint32_t left = uend - u;
+            kb1 = (uint32_t)(nkb - kb0) < left ? nkb : kb0 + (int)left;
         } else {
             tile = u;
             kb0 = 0;
             kb1 = nkb;
         }
     }
-    __device__ __forceinline__ void init(int64_t total_tiles_, int nkb_, int streamk_, int64_t w, int64_t W) {
-        total_tiles = total_tiles_;
+    __device__ __forceinline__ void init(uint32_t total_tiles, int nkb_, int streamk_, uint32_t w, uint32_t W) {
         nkb = nkb_;
         streamk = streamk_;
         if (streamk) {
-            u = range_start(total_tiles * nkb, w, W);
-            uend = range_start(total_tiles * nkb, w + 1, W);
+            u = range_start(total_tiles * (uint32_t)nkb, w, W);
+            uend = range_start(total_tiles * (uint32_t)nkb, w + 1, W);
             step = 0;
         } else {
             u = w;
@@ -131,10 +135,26 @@ struct SegIter {
     }
     __device__ __forceinline__ bool valid() const { return u < uend; }
     __device__ __forceinline__ void next() {
-        u += streamk ? (int64_t)(kb1 - kb0) : step;
+        // whole-tile mode: the last step may pass total_tiles by up to W, far below 2^32 (total_tiles < 2^31)
+        u += streamk ? (uint32_t)(kb1 - kb0) : step;
         set();
     }
 };
+
+// Where tile `tile` sits: plane, first feature, first token.  One 32-bit division when there is one plane.
+struct TileAt { int batch, tm, tn; };
+__device__ __forceinline__ TileAt tile_at(uint32_t tile, uint32_t tiles_m, uint32_t tiles_per_batch, bool one_plane) {
+    TileAt t;
+    uint32_t rem = tile;
+    t.batch = 0;
+    if (!one_plane) {
+        t.batch = (int)(tile / tiles_per_batch);
+        rem = tile - (uint32_t)t.batch * tiles_per_batch;
+    }
+    t.tn = (int)(rem / tiles_m);
+    t.tm = (int)(rem - (uint32_t)t.tn * tiles_m);
+    return t;
+}
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
     int v;
@@ -174,8 +194,8 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = NCTA == 2 ? cluster_ctarank() : 0u;  // 0 = the CTA that issues the UMMAs
-    const int64_t worker = NCTA == 2 ? (blockIdx.x >> 1) : blockIdx.x;
-    const int64_t nworkers = NCTA == 2 ? (gridDim.x >> 1) : gridDim.x;
+    const uint32_t worker = NCTA == 2 ? (blockIdx.x >> 1) : blockIdx.x;
+    const uint32_t nworkers = NCTA == 2 ? (gridDim.x >> 1) : gridDim.x;
 
     if (threadIdx.x == 0) {
         GEMM_TRACE(0); // kernel entry
@@ -207,7 +227,8 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
     else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const int64_t tiles_per_batch = (int64_t)p.tiles_m * p.tiles_n;
+    const uint32_t tiles_per_batch = (uint32_t)p.tiles_m * (uint32_t)p.tiles_n;
+    const bool one_plane = tiles_per_batch == p.total_tiles;
     // Everything above overlapped the previous kernel's tail; from here on its results are needed.
     // (Starting the weight operand's first stages above this wait, for launches whose predecessor is known
     // not to write the weights, was measured on the 32-layer encoder pass: 1 % slower, so nothing is fetched early.)
@@ -224,11 +245,10 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             bool ok = true;
             SegIter seg;
             for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); ok && seg.valid(); seg.next()) {
-                const int64_t tile = seg.tile;
-                const int batch = (int)(tile / tiles_per_batch);
-                const int rem = (int)(tile % tiles_per_batch);
-                const int m0 = (rem % p.tiles_m) * BN + (int)rank * Cfg::B_COLS;
-                const int n0 = (rem / p.tiles_m) * TILE_N + (int)rank * GEMM_BM;
+                const TileAt at = tile_at(seg.tile, (uint32_t)p.tiles_m, tiles_per_batch, one_plane);
+                const int batch = at.batch;
+                const int m0 = at.tm * BN + (int)rank * Cfg::B_COLS;
+                const int n0 = at.tn * TILE_N + (int)rank * GEMM_BM;
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
                     if (!mbar_wait(&empty[s], ph ^ 1, p.d_status, KST_WAIT_EMPTY, abort_flag)) {
                         ok = false;
@@ -272,7 +292,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             constexpr uint64_t adesc0 = make_smem_desc(16, 1024);
             constexpr uint64_t bdesc0 = make_smem_desc(Cfg::B_CHUNK_BYTES, 1024);
             int s = 0;
-            int64_t it = 0;
+            int it = 0;
             SegIter seg;
             for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); seg.valid(); seg.next(), ++it) {
                 const int acc = (int)(it & 1);
@@ -356,14 +376,14 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         uint8_t* wstg = reinterpret_cast<uint8_t*>(sbias) + EPI_WARPS * (BN / NPART) * 4 + ew * (32 * RB);
         float* wbias = reinterpret_cast<float*>(sbias) + ew * (BN / NPART);   // fp32 bias of this warp's own columns
         auto chunk_col = [&](int c) { return (NPART * c + part) * CH; };
-        int64_t it = 0;
+        int it = 0;
         SegIter seg;
         for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); seg.valid(); seg.next(), ++it) {
-            const int64_t tile = seg.tile;
-            const int batch = (int)(tile / tiles_per_batch);
-            const int rem = (int)(tile % tiles_per_batch);
-            const int m0 = (rem % p.tiles_m) * BN;
-            const int n0 = (rem / p.tiles_m) * TILE_N + (int)rank * GEMM_BM;
+            const uint32_t tile = seg.tile;
+            const TileAt at = tile_at(tile, (uint32_t)p.tiles_m, tiles_per_batch, one_plane);
+            const int batch = at.batch;
+            const int m0 = at.tm * BN;
+            const int n0 = at.tn * TILE_N + (int)rank * GEMM_BM;
             const int acc = (int)(it & 1);
             const uint32_t aph = (uint32_t)((it >> 1) & 1);
             // Stream-K roles of this segment: a contributor holds later k-blocks of a tile some other
@@ -372,9 +392,9 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             const bool contributor = seg.kb0 > 0;
             int ncontrib = 0;
             if (!contributor && seg.kb1 < seg.nkb) {
-                const int64_t units = p.total_tiles * seg.nkb, tile_end = (tile + 1) * seg.nkb;
-                while (worker + 1 + ncontrib < nworkers &&
-                       SegIter::range_start(units, worker + 1 + ncontrib, nworkers) < tile_end)
+                const uint32_t units = p.total_tiles * (uint32_t)seg.nkb, tile_end = (tile + 1) * (uint32_t)seg.nkb;
+                while (worker + 1 + (uint32_t)ncontrib < nworkers &&
+                       SegIter::range_start(units, worker + 1 + (uint32_t)ncontrib, nworkers) < tile_end)
                     ++ncontrib;
             }
             constexpr int PART_PER_WARP = (BN / NPART) * 32;             // floats one epilogue warp owns of a tile
@@ -699,8 +719,13 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
     p.strideO = nbatch > 1 ? sO : 0;
     p.tiles_m = (int)cdiv(M, BN);
     p.tiles_n = (int)cdiv(N, (int64_t)GEMM_BM * NCTA);
-    p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * nbatch;
     p.num_kb = (int)cdiv(K, GEMM_BK);
+    {
+        const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n * nbatch;
+        B200_REQUIRE(tiles * p.num_kb < ((int64_t)1 << 31), B200_EINVAL,
+                     "gemm: %lld tiles of %d k-blocks are more than one launch indexes", (long long)tiles, p.num_kb);
+        p.total_tiles = (uint32_t)tiles;
+    }
     p.bias = static_cast<const __half*>(bias);
     p.bias_per_n = bias_per_n;
     p.epilogue = epi;
@@ -734,7 +759,7 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
         }
         if (resident[ctx->device & 15] < workers_max) workers_max = resident[ctx->device & 15];
     }
-    int workers = (int)(p.total_tiles < workers_max ? p.total_tiles : workers_max);
+    int workers = (int)((int64_t)p.total_tiles < workers_max ? (int64_t)p.total_tiles : workers_max);
     p.streamk = 0;
     p.sk_part = nullptr;
     p.sk_flag = ctx->sk_flags;
