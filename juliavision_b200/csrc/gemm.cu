@@ -309,15 +309,22 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         if (kb == seg.kb0 && it == 0) GEMM_TRACE(3); // first stage landed
                         const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
                         const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+                        // low descriptor words: the constant fields | start address >> 4 (the address field cannot
+                        // carry: shared memory ends below 2^18)
+                        const uint32_t a_lo = (uint32_t)adesc0 | ((a_addr & 0x3FFFFu) >> 4);
+                        const uint32_t b_lo = (uint32_t)bdesc0 | ((b_addr & 0x3FFFFu) >> 4);
 #pragma unroll
                         for (int k = 0; k < GEMM_BK / 16; ++k) {
                             // K-major A: +16 elements of K = +32 B inside the swizzle row.
                             // MN-major B: +16 k-rows = two 8-row groups = +2048 B.
-                            const uint64_t ad = smem_desc_at(adesc0, a_addr + k * 32);
-                            const uint64_t bd = smem_desc_at(bdesc0, b_addr + k * 2048);
                             const uint32_t accum = (kb != seg.kb0 || k != 0); // a segment starts a fresh accumulator
-                            if constexpr (NCTA == 2) umma_ss_pair(d_tmem, ad, bd, idesc, accum);
-                            else umma_ss(d_tmem, ad, bd, idesc, accum);
+                            if constexpr (NCTA == 2) {
+                                umma_ss_pair_words(d_tmem, a_lo + k * 2, (uint32_t)(adesc0 >> 32), b_lo + k * 128,
+                                                   (uint32_t)(bdesc0 >> 32), idesc, k == 0 ? accum : 1u);
+                            } else {
+                                umma_ss(d_tmem, smem_desc_at(adesc0, a_addr + k * 32), smem_desc_at(bdesc0, b_addr + k * 2048),
+                                        idesc, accum);
+                            }
                         }
                         if constexpr (NCTA == 2) umma_commit_pair(&empty[s], 3); // frees the stage in both CTAs
                         else umma_commit(&empty[s]);

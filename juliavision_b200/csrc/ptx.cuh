@@ -426,6 +426,24 @@ __device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t adesc, ui
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The same with each descriptor given as two 32-bit words.  Inside a tile only the low word (the start
+// address field) changes, so the issuing thread updates it with one 32-bit add per operand; `accumulate` is
+// a compile-time constant for all but a tile's first instruction, which lets the predicate fold away.  The
+// issuer's instruction count matters: it shares its scheduler with four epilogue warps.
+__device__ __forceinline__ void umma_ss_pair_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                   uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // Arrive, once the issued UMMAs are done, on the barrier at this offset in every CTA of `mask`.
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t mask) {
     asm volatile(
