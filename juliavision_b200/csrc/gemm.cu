@@ -41,7 +41,13 @@ constexpr int SMEM_LIMIT = 232448; // 227 KB
 // NCTA = 2: a cluster of two CTAs per tile of 256 tokens x BN features (cta_group::2, UMMA M = 256):
 //           each CTA stages its own 128 token rows and BN/2 of the feature columns, so the shared
 //           memory traffic per flop halves and the tensor core is no longer starved by it.
+// BN = 512 (pairs only) is the wide tile: one accumulator of up to 512 columns instead of two of BN, two UMMAs
+//           per K step (256 columns + the rest), the tile's width a launch parameter (a multiple of 16 in
+//           (256, 512]).  It is for launches whose 256-wide tiles would need a second, mostly empty round of
+//           the workers: the width is chosen so that every tile is some worker's only one.
 template <int BN, typename OutT, int NCTA> struct GemmCfg {
+    static constexpr bool WIDE = BN == 512;
+    static_assert(!WIDE || NCTA == 2, "the wide tile is built for CTA pairs");
     static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
     static constexpr int B_CHUNK_BYTES = 64 * GEMM_BK * 2; // one 64-feature slab of the B tile
     static constexpr int B_COLS = BN / NCTA;               // feature columns this CTA stages
@@ -53,7 +59,7 @@ template <int BN, typename OutT, int NCTA> struct GemmCfg {
     static constexpr int STAGES_RAW = (SMEM_LIMIT - TAIL_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TAIL_BYTES;
-    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr int TMEM_COLS = WIDE ? 512 : (2 * BN < 32 ? 32 : 2 * BN);
     static_assert(STAGES >= 2, "ring too shallow");
     static_assert(SMEM_BYTES <= SMEM_LIMIT, "shared memory over budget");
     static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
@@ -65,6 +71,7 @@ template <int BN, typename OutT, int NCTA> struct GemmCfg {
 template <typename OutT> struct GemmParams {
     int64_t M, N, K;       // out features, tokens, reduction
     int tiles_m, tiles_n;  // feature tiles, token tiles
+    int bn;                // feature columns per tile: BN, or the wide tile's width
     uint32_t total_tiles;  // tiles_m * tiles_n * nbatch (times num_kb below 2^31, checked at launch)
     int num_kb;
     OutT* out;             // out(M,N): element (i,j) of plane b at out[b*strideO + j*ldo + i]
@@ -247,8 +254,12 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); ok && seg.valid(); seg.next()) {
                 const TileAt at = tile_at(seg.tile, (uint32_t)p.tiles_m, tiles_per_batch, one_plane);
                 const int batch = at.batch;
-                const int m0 = at.tm * BN + (int)rank * Cfg::B_COLS;
+                const int m0 = Cfg::WIDE ? at.tm * p.bn : at.tm * BN + (int)rank * Cfg::B_COLS;
                 const int n0 = at.tn * TILE_N + (int)rank * GEMM_BM;
+                // wide tile: this CTA stages its half of the first 256 columns (slabs 0, 1) and its half of the
+                // remaining n2 (slabs 2, 3: whole 64-column boxes, so up to 63 columns more than needed)
+                const int n2h = (p.bn - 256) >> 1;
+                const int slabs2 = (n2h + 63) >> 6;
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
                     if (!mbar_wait(&empty[s], ph ^ 1, p.d_status, KST_WAIT_EMPTY, abort_flag)) {
                         ok = false;
@@ -260,11 +271,21 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         // Both CTAs' bytes are counted on the leader's barrier; the leader posts
                         // the expectation for the pair.
                         const uint32_t bar = mapa_u32(smem_u32(&full[s]), 0);
-                        if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * Cfg::STAGE_BYTES);
-                        tma_load_3d_pair(sa, &tmapX, bar, kb * GEMM_BK, n0, batch);
+                        if constexpr (Cfg::WIDE) {
+                            if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * (Cfg::A_BYTES + (2 + slabs2) * Cfg::B_CHUNK_BYTES));
+                            tma_load_3d_pair(sa, &tmapX, bar, kb * GEMM_BK, n0, batch);
 #pragma unroll
-                        for (int j = 0; j < Cfg::B_COLS / 64; ++j)
-                            tma_load_3d_pair(sb + j * Cfg::B_CHUNK_BYTES, &tmapW, bar, m0 + j * 64, kb * GEMM_BK, batch);
+                            for (int j = 0; j < 2; ++j)
+                                tma_load_3d_pair(sb + j * Cfg::B_CHUNK_BYTES, &tmapW, bar, m0 + (int)rank * 128 + j * 64, kb * GEMM_BK, batch);
+                            for (int j = 0; j < slabs2; ++j)
+                                tma_load_3d_pair(sb + (2 + j) * Cfg::B_CHUNK_BYTES, &tmapW, bar, m0 + 256 + (int)rank * n2h + j * 64, kb * GEMM_BK, batch);
+                        } else {
+                            if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * Cfg::STAGE_BYTES);
+                            tma_load_3d_pair(sa, &tmapX, bar, kb * GEMM_BK, n0, batch);
+#pragma unroll
+                            for (int j = 0; j < Cfg::B_COLS / 64; ++j)
+                                tma_load_3d_pair(sb + j * Cfg::B_CHUNK_BYTES, &tmapW, bar, m0 + j * 64, kb * GEMM_BK, batch);
+                        }
                     } else {
                         mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
                         tma_load_3d(sa, &tmapX, &full[s], kb * GEMM_BK, n0, batch);
@@ -288,15 +309,16 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
         // over through a named barrier (a hardware barrier, ~100 cycles here), one per stage of the ring.
         // The whole warp runs the loop so that the barrier instruction is warp-uniform; lane 0 issues.
         if (rank == 0) {
-            constexpr uint32_t idesc = make_idesc_f16(TILE_N, BN, /*a K-major*/ 0, /*b MN-major*/ 1);
+            constexpr uint32_t idesc = make_idesc_f16(TILE_N, Cfg::WIDE ? 256 : BN, /*a K-major*/ 0, /*b MN-major*/ 1);
+            const uint32_t idesc2 = make_idesc_f16(TILE_N, p.bn - 256, 0, 1);   // wide tile: the columns past 256
             constexpr uint64_t adesc0 = make_smem_desc(16, 1024);
             constexpr uint64_t bdesc0 = make_smem_desc(Cfg::B_CHUNK_BYTES, 1024);
             int s = 0;
             int it = 0;
             SegIter seg;
             for (seg.init(p.total_tiles, p.num_kb, p.streamk, worker, nworkers); seg.valid(); seg.next(), ++it) {
-                const int acc = (int)(it & 1);
-                const uint32_t aph = (uint32_t)((it >> 1) & 1);
+                const int acc = Cfg::WIDE ? 0 : (int)(it & 1);
+                const uint32_t aph = (uint32_t)((Cfg::WIDE ? it : it >> 1) & 1);
                 bool got;
                 if constexpr (NCTA == 2) got = mbar_wait_cluster(&tempty[acc], aph ^ 1, p.d_status, KST_WAIT_TMEM_EMPTY, abort_flag);
                 else got = mbar_wait(&tempty[acc], aph ^ 1, p.d_status, KST_WAIT_TMEM_EMPTY, abort_flag);
@@ -321,6 +343,10 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                             if constexpr (NCTA == 2) {
                                 umma_ss_pair_words(d_tmem, a_lo + k * 2, (uint32_t)(adesc0 >> 32), b_lo + k * 128,
                                                    (uint32_t)(bdesc0 >> 32), idesc, k == 0 ? accum : 1u);
+                                if constexpr (Cfg::WIDE)   // slabs 2 and 3 -> accumulator columns 256..
+                                    umma_ss_pair_words(d_tmem + 256, a_lo + k * 2, (uint32_t)(adesc0 >> 32),
+                                                       b_lo + k * 128 + ((2 * Cfg::B_CHUNK_BYTES) >> 4), (uint32_t)(bdesc0 >> 32),
+                                                       idesc2, k == 0 ? accum : 1u);
                             } else {
                                 umma_ss(d_tmem, smem_desc_at(adesc0, a_addr + k * 32), smem_desc_at(bdesc0, b_addr + k * 2048),
                                         idesc, accum);
@@ -389,10 +415,10 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
             const uint32_t tile = seg.tile;
             const TileAt at = tile_at(tile, (uint32_t)p.tiles_m, tiles_per_batch, one_plane);
             const int batch = at.batch;
-            const int m0 = at.tm * BN;
+            const int m0 = at.tm * (Cfg::WIDE ? p.bn : BN);
             const int n0 = at.tn * TILE_N + (int)rank * GEMM_BM;
-            const int acc = (int)(it & 1);
-            const uint32_t aph = (uint32_t)((it >> 1) & 1);
+            const int acc = Cfg::WIDE ? 0 : (int)(it & 1);
+            const uint32_t aph = (uint32_t)((Cfg::WIDE ? it : it >> 1) & 1);
             // Stream-K roles of this segment: a contributor holds later k-blocks of a tile some other
             // worker finishes; a finisher holds the tile's first k-block and collects what the
             // following workers left for it.
@@ -499,7 +525,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmapX,   // B(K,N): {K, t
                         }
                     }
                 }
-                if (m0 + col0 >= p.M || rows_valid <= 0) continue; // nothing to write to the output
+                if (m0 + col0 >= p.M || rows_valid <= 0 || (Cfg::WIDE && col0 >= p.bn)) continue; // nothing to write to the output
 
                 // the engine must have read the previous chunk out of the slab before it is overwritten; that
                 // read ran under this chunk's tcgen05.ld and arithmetic
@@ -623,6 +649,7 @@ struct TilePick {
     int bn;      // feature columns per tile
     int ncta;    // 1: 128-token tiles, one CTA each; 2: 256-token tiles, one CTA pair each
     int streamk; // 1: equal k-block ranges per worker instead of whole tiles
+    int width;   // bn == 512 (the wide tile): feature columns per tile, a multiple of 16 in (256, 512]
 };
 
 // Tile planner.  Candidates are (BN, NCTA, whole-tile | stream-K); the estimate for each is
@@ -637,19 +664,21 @@ static int64_t streamk_workers(int64_t tiles, int64_t workers_max) {
     return 0;
 }
 
-static TilePick pick_tile(int64_t M, int64_t N, int64_t K, int64_t nbatch, int sms, bool allow_streamk = true) {
+static TilePick pick_tile(int64_t M, int64_t N, int64_t K, int64_t nbatch, int sms, bool allow_streamk = true,
+                          int epilogue = B200_EPI_NONE) {
     if (const char* f = getenv("B200_GEMM_TILE")) { // debugging aid: "<bn>x<ncta>[s]", e.g. 256x2 or 256x2s
         int bn = 0, nc = 0;
         char sk = 0;
         const int got = sscanf(f, "%dx%d%c", &bn, &nc, &sk);
         if (got >= 2 && (bn == 256 || bn == 128 || (bn == 64 && nc == 1)) && (nc == 1 || nc == 2))
-            return {bn, nc, allow_streamk && got == 3 && sk == 's'};
+            return {bn, nc, allow_streamk && got == 3 && sk == 's', 0};
+        if (got >= 2 && bn > 256 && bn <= 512 && bn % 16 == 0 && nc == 2) return {512, 2, 0, bn};   // "<width>x2": the wide tile
     }
     struct Cand { int bn, ncta; double t_kb; };
     const Cand cands[5] = {{256, 2, 0.39}, {128, 2, 0.38}, {256, 1, 0.50}, {128, 1, 0.38}, {64, 1, 0.32}};
     const int64_t nkb = cdiv(K, GEMM_BK);
     const double t_tile = 2.0, t_fix = 8.0;  // measured: partial dump + fence + flag + read-back
-    TilePick best{256, 1, 0};
+    TilePick best{256, 1, 0, 0};
     double best_cost = 1e300;
     for (const Cand& c : cands) {   // whole-tile schedules first: stream-K has to beat the best of them clearly
         const int64_t tiles = cdiv(M, c.bn) * cdiv(N, (int64_t)GEMM_BM * c.ncta) * nbatch;
@@ -657,7 +686,29 @@ static TilePick pick_tile(int64_t M, int64_t N, int64_t K, int64_t nbatch, int s
         const double dp = (double)waves * ((double)nkb * c.t_kb + t_tile);
         if (dp < best_cost - 1e-9) {
             best_cost = dp;
-            best = {c.bn, c.ncta, 0};
+            best = {c.bn, c.ncta, 0, 0};
+        }
+    }
+    {
+        // The wide tile: when 256-wide pair tiles need more than one round of the workers, a width in
+        // (256, 512] that makes every tile some worker's only one.  Measured on B200 (1500 tokens, K = 1280,
+        // microseconds): 7 + k-blocks x 0.3 x width/256 (two UMMAs per K step; never below 1.25 tile-widths,
+        // where issuing them is what takes the time) + 0.25 per 64 columns of epilogue, none of which anything
+        // hides (0.85 with GELU).  It has to beat the whole-tile estimate by a margin to be taken.
+        const int64_t workers = sms / 2;
+        const int64_t token_tiles = cdiv(N, (int64_t)GEMM_BM * 2) * nbatch;
+        const int64_t fm = workers / token_tiles;   // feature tiles a single round has room for
+        if (fm >= 1 && cdiv(M, 256) * token_tiles > workers) {
+            const int64_t width = cdiv(cdiv(M, fm), 16) * 16;
+            if (width > 256 && width <= 512) {
+                const double rel = (double)width / 256.0;
+                const bool gelu = epilogue == B200_EPI_GELU || epilogue == B200_EPI_GELU_TANH;
+                const double wide = 7.0 + (double)nkb * 0.3 * (rel < 1.25 ? 1.25 : rel) + (gelu ? 0.85 : 0.25) * (double)width / 64.0;
+                if (wide < 0.92 * best_cost) {
+                    best_cost = wide;
+                    best = {512, 2, 0, (int)width};
+                }
+            }
         }
     }
     best_cost *= 0.85;
@@ -674,7 +725,7 @@ static TilePick pick_tile(int64_t M, int64_t N, int64_t K, int64_t nbatch, int s
             const double sk = (double)(tiles * nkb) / (double)skw * c.t_kb + t_tile + t_fix;
             if (sk < best_cost - 1e-9) {
                 best_cost = sk;
-                best = {c.bn, c.ncta, 1};
+                best = {c.bn, c.ncta, 1, 0};
             }
         }
     }
@@ -684,8 +735,12 @@ static TilePick pick_tile(int64_t M, int64_t N, int64_t K, int64_t nbatch, int s
 template <int BN, typename OutT, int NCTA>
 static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
                      const void* B, int64_t ldb, const void* bias, int bias_per_n, void* out, int64_t ldo,
-                     int epi, int64_t nbatch, int64_t sA, int64_t sB, int64_t sO, int streamk) {
+                     int epi, int64_t nbatch, int64_t sA, int64_t sB, int64_t sO, int streamk, int width) {
     using Cfg = GemmCfg<BN, OutT, NCTA>;
+    if (Cfg::WIDE) {
+        B200_REQUIRE(width > 256 && width <= 512 && width % 16 == 0, B200_EINVAL, "gemm: wide tile of %d columns", width);
+        streamk = 0;
+    }
     static bool attr_done[16] = {};
     auto kern = gemm_f16_tc_kernel<BN, OutT, NCTA>;
     if (!attr_done[ctx->device & 15]) {
@@ -724,7 +779,8 @@ static int launch_tc(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void*
     p.out = static_cast<OutT*>(out);
     p.ldo = ldo;
     p.strideO = nbatch > 1 ? sO : 0;
-    p.tiles_m = (int)cdiv(M, BN);
+    p.bn = Cfg::WIDE ? width : BN;
+    p.tiles_m = (int)cdiv(M, p.bn);
     p.tiles_n = (int)cdiv(N, (int64_t)GEMM_BM * NCTA);
     p.num_kb = (int)cdiv(K, GEMM_BK);
     {
@@ -815,11 +871,14 @@ int b200_gemm_f16_plan(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, int64_t n
     B200_REQUIRE(M >= 1 && N >= 1 && K >= 1 && nbatch >= 1, B200_DECLINE_EXTENT, "gemm_plan: empty extent");
     const int sms = ctx->prop.multiProcessorCount;
     const TilePick t = pick_tile(M, N, K, nbatch, sms);
-    const int bn = t.bn;
+    const int bn = t.bn == 512 ? t.width : t.bn;
     plan->block_m = GEMM_BM * t.ncta;
     plan->block_n = bn;
     plan->block_k = GEMM_BK;
-    if (t.ncta == 2) {
+    if (t.bn == 512) {
+        plan->stages = GemmCfg<512, __half, 2>::STAGES;
+        plan->smem_bytes = GemmCfg<512, __half, 2>::SMEM_BYTES;
+    } else if (t.ncta == 2) {
         plan->stages = bn == 256 ? GemmCfg<256, __half, 2>::STAGES : GemmCfg<128, __half, 2>::STAGES;
         plan->smem_bytes = bn == 256 ? GemmCfg<256, __half, 2>::SMEM_BYTES : GemmCfg<128, __half, 2>::SMEM_BYTES;
     } else {
@@ -884,17 +943,19 @@ int gemm_f16_run(b200_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, 
         B200_CUDA(cudaGetLastError());
         return B200_OK;
     }
-    const TilePick t = pick_tile(M, N, K, nbatch, ctx->prop.multiProcessorCount, use_workspace != 0);
+    const TilePick t = pick_tile(M, N, K, nbatch, ctx->prop.multiProcessorCount, use_workspace != 0, epilogue);
 #define GEMM_GO(BN_, T_, NC_)                                                                                     \
     return launch_tc<BN_, T_, NC_>(ctx, M, N, K, A, lda, B, ldb, bias, bias_per_n, out, ldo, epilogue, nbatch, strideA, \
-                                   strideB, strideO, t.streamk)
+                                   strideB, strideO, t.streamk, t.width)
     if (out_dtype == B200_F16) {
+        if (t.bn == 512) GEMM_GO(512, __half, 2);
         if (t.ncta == 2 && t.bn == 256) GEMM_GO(256, __half, 2);
         if (t.ncta == 2) GEMM_GO(128, __half, 2);
         if (t.bn == 256) GEMM_GO(256, __half, 1);
         if (t.bn == 128) GEMM_GO(128, __half, 1);
         GEMM_GO(64, __half, 1);
     } else {
+        if (t.bn == 512) GEMM_GO(512, float, 2);
         if (t.ncta == 2 && t.bn == 256) GEMM_GO(256, float, 2);
         if (t.ncta == 2) GEMM_GO(128, float, 2);
         if (t.bn == 256) GEMM_GO(256, float, 1);

@@ -136,12 +136,13 @@ def test_linearity_at_full_size(ctx):
     assert np.array_equal(y1 + y2, y12)           # integer-valued: every partial sum is exact
 
 
-@pytest.mark.parametrize("tile", ["256x2", "128x2", "256x1", "128x1", "64x1", "256x2s", "128x2s", "256x1s", "64x1s"])
+@pytest.mark.parametrize("tile", ["256x2", "128x2", "256x1", "128x1", "64x1", "256x2s", "128x2s", "256x1s", "64x1s",
+                                  "272x2", "320x2", "384x2", "432x2", "512x2"])
 def test_every_tile_shape_and_schedule(ctx, ora, tile, monkeypatch):
     """The planner picks one (tile width, CTAs per tile, schedule) per call; the debugging override
     forces each of them in turn — CTA pairs, single CTAs, whole-tile and stream-K schedules (a
-    trailing `s`) — on shapes with ragged tails, several tiles per worker and tiles cut across
-    workers.  All must agree with the oracle like the planner's own choice does."""
+    trailing `s`), the wide single-accumulator tile at several widths (a width above 256) — on shapes
+    with ragged tails, several tiles per worker and tiles cut across workers.  All must agree with the oracle like the planner's own choice does."""
     monkeypatch.setenv("B200_GEMM_TILE", tile)
     rng = np.random.default_rng(hash(tile) % 1000)
     for tokens, out, K in ((1500, 1280, 1280), (700, 5120, 640), (300, 1000, 4096), (4096, 3072, 768)):
