@@ -49,7 +49,7 @@ def peaks():
 # launches, from one profiler capture of that pass (a profiler cannot run inside a timed benchmark, so
 # the figure is carried as a constant; GEMM_DRAM_CAPTURE says which kernel version it was taken from).
 GEMM_DRAM_BYTES_PER_LAUNCH = 16_619_000
-GEMM_DRAM_CAPTURE = "ncu, one encoder pass, GEMM kernel with the relay warp (608 threads), 2026-11-25"
+GEMM_DRAM_CAPTURE = "ncu, one encoder pass, GEMM kernels as built (wide tile for q/k/v, 608 threads), 2026-11-25"
 
 
 class ClockSampler:
