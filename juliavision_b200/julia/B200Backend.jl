@@ -117,6 +117,7 @@ struct MMScalarPlan end
 """Fused single-pass attention on tcgen05."""
 struct FlashTCPlan end
 struct AttnScalarPlan end
+struct TwoGemmPlan end     # head dims above 128 (multiples of 8): the two-GEMM route inside the library
 
 dtcode(::Type{Float16}) = Cint(0)
 dtcode(::Type{Float32}) = Cint(1)
@@ -201,11 +202,17 @@ function sdpaplan(ctx::Ctx{B200Backend}, q, k, v, bias)
                (Int64, Int64, Int64, Int64, Int64, Ptr{Int64}, Ptr{Int64}, Ptr{Int64}, Cint),
                E, Lq, Lk, H, B, st(q), st(k), st(v), 0)
     rc == OK && return (FlashTCPlan(), k, v)
-    rc in (18, 21) && return (AttnScalarPlan(), k, v)
+    if rc in (18, 21)
+        # head dims above 128: S = K'Q, softmax over the keys, O = V P on the GEMM kernel (route 1), else scalar
+        route = ccall((:b200_attention_f16_route, LIB), Cint,
+                      (Int64, Int64, Int64, Int64, Int64, Ptr{Int64}, Ptr{Int64}, Ptr{Int64}),
+                      E, Lq, Lk, H, B, st(q), st(k), st(v))
+        return (route == 1 ? TwoGemmPlan() : AttnScalarPlan(), k, v)
+    end
     (Decline(get(DECLINE, Int(rc), :extent)), k, v)
 end
 
-function sdpa!(ctx, ::Union{FlashTCPlan,AttnScalarPlan}, out, q, k, v, bias, scale)
+function sdpa!(ctx, ::Union{FlashTCPlan,TwoGemmPlan,AttnScalarPlan}, out, q, k, v, bias, scale)
     E, Lq, H, B = size(q); Lk = size(k, 2)
     out === nothing && (out = KernelAbstractions.allocate(ctx.backend, accum(eltype(q)), E, Lq, H, B))
     # `out` may be any (E, Lq, H, B) view with E contiguous: a token-major destination folds the
@@ -302,15 +309,39 @@ replay!(b::B200Backend, g::Ptr{Cvoid}) = check(ccall((:b200_graph_launch, LIB), 
 
 # ------------------------------------------------------------------ convolution! (conv.jl:100-145)
 function convolution!(ctx::Ctx{B200Backend}, out, x, w, bias, stride, padding, dilation, groups; act = :none)
-    groups == 1 || error("convolution!: Decline(:groups) on the B200 backend")
     W, H, Cin, N = size(x); KW, KH, _, Cout = size(w)
-    check(ccall((:b200_conv2d_f16, LIB), Cint,
+    check(ccall((:b200_conv2d_grouped_f16, LIB), Cint,
                 (Ptr{Cvoid}, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64,
-                 Int64, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Cint, Cint),
+                 Int64, Int64, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Cint, Cint),
                 ctx.backend.handle, W, H, Cin, N, KW, KH, Cout, stride[1], stride[2], padding[1], padding[2],
-                dilation[1], dilation[2], pointer(x), pointer(w), bias === nothing ? C_NULL : pointer(bias),
+                dilation[1], dilation[2], groups, pointer(x), pointer(w), bias === nothing ? C_NULL : pointer(bias),
                 pointer(out), dtcode(eltype(out)), act === :relu ? 1 : act === :gelu ? 2 : 0))
     out
 end
+
+# ------------------------------------------------------------------ convolutiontranspose! (conv.jl:247-290)
+# shufflecase (stride == kernel, nothing else set, one group) runs as a GEMM + depth-to-space inside the
+# library; every other geometry as the deterministic gather.  w is (KW, KH, Cout ÷ groups, Cin).
+function convolutiontranspose!(ctx::Ctx{B200Backend}, out, x, w, bias, stride, padding, dilation, outpad, groups)
+    W, H, Cin, N = size(x); KW, KH, Cog, _ = size(w)
+    check(ccall((:b200_convtranspose2d_f16, LIB), Cint,
+                (Ptr{Cvoid}, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64, Int64,
+                 Int64, Int64, Int64, Int64, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Cint),
+                ctx.backend.handle, W, H, Cin, N, KW, KH, Cog * groups, stride[1], stride[2], padding[1], padding[2],
+                dilation[1], dilation[2], outpad[1], outpad[2], groups, pointer(x), pointer(w),
+                bias === nothing ? C_NULL : pointer(bias), pointer(out), dtcode(eltype(out))))
+    out
+end
+
+# ------------------------------------------------------------------ Diagnostics (context.jl:162-221)
+# optimes: bracket an op with the context's event timer (milliseconds on the device).
+function optime(f, b::B200Backend)
+    check(ccall((:b200_timer_start, LIB), Cint, (Ptr{Cvoid},), b.handle))
+    f()
+    ms = Ref{Cfloat}(0)
+    check(ccall((:b200_timer_stop, LIB), Cint, (Ptr{Cvoid}, Ref{Cfloat}), b.handle, ms))
+    Float64(ms[])
+end
+launchcount(b::B200Backend) = ccall((:b200_launch_count, LIB), Int64, (Ptr{Cvoid},), b.handle)
 
 end # module
