@@ -507,7 +507,7 @@ def run_hiera(args):
     e2e_serial_ms = ctx.timer_stop() / args.steps
     barrier()
     # copies on the copy lane, under the neighbouring passes (see StreamedPass)
-    streamed = jv.StreamedPass(ctx, graph, model.image, model.y)
+    streamed = jv.StreamedPass(ctx, model.forward, model.image, model.y)
     streamed.run([hx.value] * 3, [hy.value] * 3)
     ctx.synchronize()
     barrier()
@@ -707,7 +707,7 @@ def main():
 
     # ---- the same, as a caller that streams inputs would run it: every step's input still goes up from pinned
     # host memory and every step's result still comes down, but on the copy lane, under the neighbouring passes
-    streamed = jv.StreamedPass(ctx, graph, enc.xin, enc.y)
+    streamed = jv.StreamedPass(ctx, enc.forward, enc.xin, enc.y)
     streamed.run([hx.value] * 3, [hy.value] * 3)
     ctx.synchronize()
     barrier()

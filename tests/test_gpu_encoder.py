@@ -159,12 +159,17 @@ def test_streamed_passes_give_each_input_its_own_result(ctx):
         C.memset(b.value, 0xFF, nbytes)
         hin.append(a.value)
         hout.append(b.value)
-    sp = jv.StreamedPass(ctx, g, enc.xin, enc.y)
-    sp.run(hin, hout)
-    ctx.synchronize()
-    for i in range(n):
-        got = np.frombuffer((C.c_char * nbytes).from_address(hout[i]), dtype=np.float16).reshape(cfg.tokens, cfg.d_model)
-        assert np.array_equal(got, want[i]), f"pass {i}"
+    # both forms: an already recorded graph with the staging copies around it, and the launching callable, from
+    # which StreamedPass records one graph per staging pair with the copies inside
+    for fwd in (g, enc.forward):
+        for p_ in hout:
+            C.memset(p_, 0xFF, nbytes)
+        sp = jv.StreamedPass(ctx, fwd, enc.xin, enc.y)
+        sp.run(hin, hout)
+        ctx.synchronize()
+        for i in range(n):
+            got = np.frombuffer((C.c_char * nbytes).from_address(hout[i]), dtype=np.float16).reshape(cfg.tokens, cfg.d_model)
+            assert np.array_equal(got, want[i]), f"pass {i}"
     for p_ in hin + hout:
         _lib.lib().b200_host_free(C.c_void_p(p_))
 
