@@ -201,13 +201,24 @@ ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half*
 
     float v[VPL][VN];
     float s = 0.f;
+    // every load of the row first, then the arithmetic: one round trip for the row whatever the compiler would
+    // have made of loads and stores through the same pointer
+    uint4 xraw[VPL], hraw[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int vi = lane + 32 * i;
+        if (vi < nvec) {
+            xraw[i] = *(reinterpret_cast<const uint4*>(xr) + vi);
+            hraw[i] = __ldg(reinterpret_cast<const uint4*>(hr) + vi);
+        }
+    }
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
         const int vi = lane + 32 * i;
         if (vi < nvec) {
             Vec16<__half> a, b;
-            a.raw = *(reinterpret_cast<const uint4*>(xr) + vi);
-            b.raw = __ldg(reinterpret_cast<const uint4*>(hr) + vi);
+            a.raw = xraw[i];
+            b.raw = hraw[i];
             float fa[VN], fb[VN];
             a.to_f32(fa);
             b.to_f32(fb);
