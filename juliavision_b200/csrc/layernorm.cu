@@ -75,7 +75,10 @@ __device__ __forceinline__ float group_sum(float v) {
 // One warp per group; lane l owns vectors l, l+32, ... (VPL of them at most).  Narrow groups (at most
 // 16 or 8 vectors, VPL = 1) share a warp, LPG lanes each, so that no lane idles; the sums are the same
 // butterflies with the empty upper steps left out, hence the same bits.
-template <typename InT, typename OutT, int VPL, int LPG = 32>
+// LAT: the latency form, for launches small enough that every CTA is resident at once and what the kernel takes
+// is a chain of round trips, not bytes (the encoder's 1500 rows): everything the row needs is asked for up front.
+// It costs ~40 registers; launches of many waves, which want occupancy, take the lean form.
+template <typename InT, typename OutT, int VPL, int LPG = 32, bool LAT = false>
 __global__ void __launch_bounds__(128)
 ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restrict__ mean,
                float* __restrict__ rstd, const InT* __restrict__ gamma,
@@ -89,7 +92,7 @@ ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restr
     // gamma and beta are weights, not the previous kernel's output: narrow rows fetch them while the CTA still
     // waits for that kernel, so that the normalised row does not wait for them at the end (measured on the
     // encoder pass with the add + layer-norm kernel below: 3.45 -> 3.37 ms).
-    constexpr bool HOIST = VPL <= 6;
+    constexpr bool HOIST = LAT && VPL <= 6;
     uint4 gw[HOIST ? VPL : 1], bw[HOIST ? VPL : 1];
     if constexpr (HOIST) {
 #pragma unroll
@@ -170,7 +173,7 @@ ln_warp_kernel(const InT* __restrict__ a, OutT* __restrict__ out, float* __restr
 // Bit-identical to running add.Tensor, clamp.default and native_layer_norm one after another
 // (each rounds to fp16 where the separate ops would), but x and h are read once and the three
 // launches become one.
-template <int VPL, int LPG = 32>
+template <int VPL, int LPG = 32, bool LAT = false>
 __global__ void __launch_bounds__(128)
 ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half* __restrict__ out,
                    float* __restrict__ mean, float* __restrict__ rstd, const __half* __restrict__ gamma,
@@ -184,7 +187,7 @@ ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half*
     // gamma and beta are weights, not the previous kernel's output: they are fetched while this CTA still waits
     // for it, so that the normalised row does not wait for them at the end.
     // (Rows of up to 1536 elements; wider ones would spill, and read them where they are used.)
-    constexpr bool HOIST = VPL <= 6;
+    constexpr bool HOIST = LAT && VPL <= 6;
     uint4 gw[HOIST ? VPL : 1], bw[HOIST ? VPL : 1];
     if constexpr (HOIST) {
 #pragma unroll
@@ -203,13 +206,16 @@ ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half*
     float s = 0.f;
     // every load of the row first, then the arithmetic: one round trip for the row whatever the compiler would
     // have made of loads and stores through the same pointer
-    uint4 xraw[VPL], hraw[VPL];
+    // (the latency form; the lean one reads each vector where it uses it)
+    uint4 xraw[HOIST ? VPL : 1], hraw[HOIST ? VPL : 1];
+    if constexpr (HOIST) {
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-        const int vi = lane + 32 * i;
-        if (vi < nvec) {
-            xraw[i] = *(reinterpret_cast<const uint4*>(xr) + vi);
-            hraw[i] = __ldg(reinterpret_cast<const uint4*>(hr) + vi);
+        for (int i = 0; i < VPL; ++i) {
+            const int vi = lane + 32 * i;
+            if (vi < nvec) {
+                xraw[i] = *(reinterpret_cast<const uint4*>(xr) + vi);
+                hraw[i] = __ldg(reinterpret_cast<const uint4*>(hr) + vi);
+            }
         }
     }
 #pragma unroll
@@ -217,8 +223,13 @@ ln_add_warp_kernel(__half* __restrict__ x, const __half* __restrict__ h, __half*
         const int vi = lane + 32 * i;
         if (vi < nvec) {
             Vec16<__half> a, b;
-            a.raw = xraw[i];
-            b.raw = hraw[i];
+            if constexpr (HOIST) {
+                a.raw = xraw[i];
+                b.raw = hraw[i];
+            } else {
+                a.raw = *(reinterpret_cast<const uint4*>(xr) + vi);
+                b.raw = __ldg(reinterpret_cast<const uint4*>(hr) + vi);
+            }
             float fa[VN], fb[VN];
             a.to_f32(fa);
             b.to_f32(fb);
@@ -346,9 +357,17 @@ static int launch_ln(b200_ctx* ctx, int64_t groups, int64_t C, const void* a, vo
         const int vpl = (nvec + 31) / 32;
         const int wpb = 4;
         dim3 grid((unsigned)cdiv(groups, wpb)), block(32 * wpb);
+        // few enough rows that every CTA is resident at once: the latency form (see the kernel)
+        const bool lat = groups <= (int64_t)4 * wpb * ctx->prop.multiProcessorCount;
 #define LN_GO(V)                                                                                            \
-    B200_CUDA(launch_dep(ln_warp_kernel<InT, OutT, V>, grid, block, 0, ctx->stream, 1, ap, op, mean, rstd, gp, bp, \
-                         groups, (int)C, eps))
+    do {                                                                                                    \
+        if (lat)                                                                                            \
+            B200_CUDA(launch_dep(ln_warp_kernel<InT, OutT, V, 32, true>, grid, block, 0, ctx->stream, 1, ap, op, mean, rstd, gp, \
+                                 bp, groups, (int)C, eps));                                                 \
+        else                                                                                                \
+            B200_CUDA(launch_dep(ln_warp_kernel<InT, OutT, V>, grid, block, 0, ctx->stream, 1, ap, op, mean, rstd, gp, bp, \
+                                 groups, (int)C, eps));                                                     \
+    } while (0)
 #define LN_GO_SHARED(L)                                                                                     \
     B200_CUDA(launch_dep(ln_warp_kernel<InT, OutT, 1, L>, dim3((unsigned)cdiv(groups, wpb * (32 / L))), block, 0,   \
                          ctx->stream, 1, ap, op, mean, rstd, gp, bp, groups, (int)C, eps))
@@ -400,10 +419,18 @@ extern "C" int b200_add_layernorm_f16(b200_ctx* ctx, int64_t groups, int64_t C, 
     }
     const int nvec = (int)(C / 8), vpl = (nvec + 31) / 32, wpb = 4;
     dim3 grid((unsigned)cdiv(groups, wpb)), block(32 * wpb);
+    const bool lat = groups <= (int64_t)4 * wpb * ctx->prop.multiProcessorCount;   // every CTA resident at once: the latency form
 #define LNA_GO(V)                                                                                                 \
-    B200_CUDA(launch_dep(ln_add_warp_kernel<V>, grid, block, 0, ctx->stream, 1, (__half*)x, (const __half*)h,           \
-                         (__half*)out, mean, rstd, (const __half*)gamma, (const __half*)beta, groups, (int)C, eps, \
-                         use_clamp, lo, hi))
+    do {                                                                                                          \
+        if (lat)                                                                                                  \
+            B200_CUDA(launch_dep(ln_add_warp_kernel<V, 32, true>, grid, block, 0, ctx->stream, 1, (__half*)x, (const __half*)h, \
+                                 (__half*)out, mean, rstd, (const __half*)gamma, (const __half*)beta, groups, (int)C, eps, \
+                                 use_clamp, lo, hi));                                                             \
+        else                                                                                                      \
+            B200_CUDA(launch_dep(ln_add_warp_kernel<V>, grid, block, 0, ctx->stream, 1, (__half*)x, (const __half*)h,   \
+                                 (__half*)out, mean, rstd, (const __half*)gamma, (const __half*)beta, groups, (int)C, eps, \
+                                 use_clamp, lo, hi));                                                             \
+    } while (0)
 #define LNA_GO_SHARED(L)                                                                                          \
     B200_CUDA(launch_dep(ln_add_warp_kernel<1, L>, dim3((unsigned)cdiv(groups, wpb * (32 / L))), block, 0, ctx->stream, 1, \
                          (__half*)x, (const __half*)h, (__half*)out, mean, rstd, (const __half*)gamma,             \
