@@ -93,6 +93,23 @@ def test_batched(ctx, ora):
     assert relerr(got, ref) < TOL, describe(got, ref, TOL)
 
 
+@pytest.mark.parametrize("tile", ["320x2", "256x2s", "128x1"])
+def test_batched_under_forced_schedules(ctx, ora, tile, monkeypatch):
+    """Several planes through the wide tile, a split along K and single-CTA tiles: the plane index is the third
+    coordinate of every tensor map and part of the tile index, whatever the schedule."""
+    monkeypatch.setenv("B200_GEMM_TILE", tile)
+    rng = np.random.default_rng(17)
+    nb, m, k, n = 3, 300, 640, 712
+    a = (rng.standard_normal((nb, m, k)) * 0.25).astype(np.float16)
+    b = (rng.standard_normal((nb, k, n)) * 0.25).astype(np.float16)
+    A, B = ctx.toback(b), ctx.toback(a)
+    out = ctx.allocate(np.float16, n, m, nb)
+    ctx.fill_bytes(out, 0xFF)
+    jv.batchedmatmul_(ctx, out, A, B)
+    ctx.synchronize()
+    assert relerr(out.to_host(), ora.bmm(a, b)) < TOL
+
+
 def test_padded_leading_dimensions(ctx, ora):
     """Views into wider buffers (ld > extent): the bytes outside the view stay untouched."""
     rng = np.random.default_rng(8)
