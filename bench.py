@@ -492,6 +492,17 @@ def run_hiera(args):
     ms_step = ctx.timer_stop() / args.steps
     barrier()
 
+    # end to end with the copies on the copy lane, under the neighbouring passes (see StreamedPass); timed next to the
+    # device-resident figure so that both see the GPU in the same power state
+    streamed = jv.StreamedPass(ctx, model.forward, model.image, model.y)
+    streamed.run([hx.value] * 3, [hy.value] * 3)
+    ctx.synchronize()
+    barrier()
+    ctx.timer_start()
+    streamed.run([hx.value] * args.steps, [hy.value] * args.steps)
+    streamed.downloaded[(args.steps - 1) & 1].wait_on(0)
+    e2e_ms = ctx.timer_stop() / args.steps
+    barrier()
     def e2e_step():
         _lib.check(_lib.lib().b200_upload_async(ctx.handle, model.image.ptr, hx, img.nbytes))
         graph.replay()
@@ -505,16 +516,6 @@ def run_hiera(args):
     for _ in range(args.steps):
         e2e_step()
     e2e_serial_ms = ctx.timer_stop() / args.steps
-    barrier()
-    # copies on the copy lane, under the neighbouring passes (see StreamedPass)
-    streamed = jv.StreamedPass(ctx, model.forward, model.image, model.y)
-    streamed.run([hx.value] * 3, [hy.value] * 3)
-    ctx.synchronize()
-    barrier()
-    ctx.timer_start()
-    streamed.run([hx.value] * args.steps, [hy.value] * args.steps)
-    streamed.downloaded[(args.steps - 1) & 1].wait_on(0)
-    e2e_ms = ctx.timer_stop() / args.steps
     barrier()
     clocks = sampler.stop()
     # dominant kernel family of the pass alone: its GEMM launches replayed back to back on the pass's buffers
